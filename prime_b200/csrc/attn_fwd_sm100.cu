@@ -1,0 +1,336 @@
+// Causal / document-masked GQA flash attention forward for sm_100a on tcgen05 + TMEM + TMA.
+//
+// Input is the fused, already rotated projection buffer qkv[M, (H + 2*KV) * HD]:
+// q head h at column h*HD, k head g at (H + g)*HD, v head g at (H + KV + g)*HD.
+// The M rows are a packed token stream; seq_start[m] is the first row query m may attend to
+// (start of its batch row or, with sequence packing, of its document), and m itself is the
+// last (causal). This replaces repeat_kv + FlexAttention/SDPA of the reference
+// (models/llama/model.py:147-156, 168-198, 282-302): KV heads are indexed, never expanded,
+// and the document mask comes from seq_start, not from a BlockMask.
+//
+// One CTA = one 128-row query tile of one head. Roles: warp 0 TMA producer, warp 1 MMA issuer
+// (owns TMEM), warps 2-5 softmax (one thread per query row: row max / sum are thread-local).
+//   S = Q K^T            -> TMEM [128 x 128] fp32
+//   P = exp2(S*c - m*c)  -> bf16 in shared memory (128B-swizzled, K-major for the PV MMA)
+//   O_j = P V            -> TMEM [128 x HD] fp32, folded into a register accumulator with the
+//                           usual online-softmax rescale
+// Outputs: o[M, H*HD] bf16 and lse2[H, M] = log2-sum-exp of the scaled scores (log2 units).
+#include "common.cuh"
+
+namespace pb {
+
+struct AttnFwdParams {
+    int M, H, KV;
+    const int* seq_start;
+    __nv_bfloat16* O;
+    long long o_stride;
+    float* lse2;
+    float scale_log2;   // softmax scale * log2(e)
+    int* status;
+};
+
+template <int HD>
+struct AttnFwdCfg {
+    static constexpr int TILE_BYTES = 128 * HD * 2;          // one Q / K / V tile
+    static constexpr int P_BYTES = 128 * 128 * 2;
+    static constexpr int KV_STAGES = 2;
+    static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 1024 + 128;
+    static constexpr int TMEM_COLS = 256;                    // S: 128 cols, O: HD cols
+};
+
+template <int HD>
+__global__ void __launch_bounds__(192, (HD == 64 ? 2 : 1))
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
+    using Cfg = AttnFwdCfg<HD>;
+    constexpr int NB = HD / 64;   // 64-column swizzle blocks per tile
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sQ = base;
+    const uint32_t sK = sQ + Cfg::TILE_BYTES;                           // [2]
+    const uint32_t sV = sK + Cfg::KV_STAGES * Cfg::TILE_BYTES;           // [2]
+    const uint32_t sP = sV + Cfg::KV_STAGES * Cfg::TILE_BYTES;
+    uint8_t* gP = gen + (sP - base);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gen + (sP - base) + Cfg::P_BYTES);
+    const uint32_t bar_q = smem_u32(bars);
+    const uint32_t bar_kfull = bar_q + 8;        // [2]
+    const uint32_t bar_vfull = bar_kfull + 16;   // [2]
+    const uint32_t bar_kvempty = bar_vfull + 16; // [2]
+    const uint32_t bar_sfull = bar_kvempty + 16;
+    const uint32_t bar_pfull = bar_sfull + 8;
+    const uint32_t bar_ofull = bar_pfull + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_tile = gridDim.x - 1 - blockIdx.x;   // heaviest (latest) tiles first
+    const int head = blockIdx.y;
+    const int kvh = head / (p.H / p.KV);
+    const int q0 = q_tile * 128;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_q, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar_kfull + 8 * s, 1);
+            mbar_init(bar_vfull + 8 * s, 1);
+            mbar_init(bar_kvempty + 8 * s, 1);
+        }
+        mbar_init(bar_sfull, 1);
+        mbar_init(bar_pfull, 4);
+        mbar_init(bar_ofull, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tm);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tS = tmem_base, tO = tmem_base + 128;
+
+    // kv tile range: from the tile holding the first row's sequence start up to the diagonal
+    const int first_start = p.seq_start[min(q0, p.M - 1)];
+    const int kv_lo = first_start / 128;
+    const int kv_hi = q_tile;                      // inclusive
+    const int n_kv = kv_hi - kv_lo + 1;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(bar_q, Cfg::TILE_BYTES);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) tma_load_2d(sQ + b * 16384, &tm, bar_q, head * HD + 64 * b, q0);
+        }
+        bool ok = true;
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int st = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            ok = mbar_wait(bar_kvempty + 8 * st, ph ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (lane == 0) {
+                const int kv0 = (kv_lo + j) * 128;
+                mbar_expect_tx(bar_kfull + 8 * st, Cfg::TILE_BYTES);
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                    tma_load_2d(sK + st * Cfg::TILE_BYTES + b * 16384, &tm, bar_kfull + 8 * st, (p.H + kvh) * HD + 64 * b, kv0);
+                mbar_expect_tx(bar_vfull + 8 * st, Cfg::TILE_BYTES);
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                    tma_load_2d(sV + st * Cfg::TILE_BYTES + b * 16384, &tm, bar_vfull + 8 * st, (p.H + p.KV + kvh) * HD + 64 * b, kv0);
+            }
+            __syncwarp();
+        }
+        if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(10000);
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
+        auto issue_s = [&](int st) {
+            const uint32_t kb = sK + st * Cfg::TILE_BYTES;
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k) {
+                const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+                umma_f16_ss(tS, umma_smem_desc(sQ + off, 16, 1024), umma_smem_desc(kb + off, 16, 1024), idesc_s, k ? 1u : 0u);
+            }
+            umma_commit(bar_sfull);
+        };
+        bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            ok = mbar_wait(bar_kfull, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            if (lane == 0) issue_s(0);
+            __syncwarp();
+        }
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int st = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            ok = mbar_wait(bar_pfull, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ok = mbar_wait(bar_vfull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t vb = sV + st * Cfg::TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {   // 128 kv rows, 16 per step
+                    const uint64_t da = umma_smem_desc(sP + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+                    const uint64_t db = umma_smem_desc(vb + k * 2048, 16384, 1024);
+                    umma_f16_ss(tO, da, db, idesc_o, k ? 1u : 0u);
+                }
+                umma_commit(bar_ofull);
+                umma_commit(bar_kvempty + 8 * st);
+            }
+            __syncwarp();
+            if (j + 1 < n_kv) {
+                const int st1 = (j + 1) & 1;
+                const uint32_t ph1 = ((j + 1) >> 1) & 1;
+                ok = mbar_wait(bar_kfull + 8 * st1, ph1, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) issue_s(st1);
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------ softmax warps ------------------------------
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;           // row within the tile == TMEM lane
+        const int row = q0 + r;
+        const uint32_t lane_off = uint32_t(quad * 32) << 16;
+        const int my_start = p.seq_start[min(row, p.M - 1)];
+        const int tile_last_start = p.seq_start[min(q0 + 127, p.M - 1)];
+        const float c = p.scale_log2;
+        float m_run = -INFINITY, l_run = 0.f;
+        float o_acc[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int kv0 = (kv_lo + j) * 128;
+            ok = mbar_wait(bar_sfull, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const bool need_mask = (kv0 + 127 > q0) || (kv0 < tile_last_start);
+            // pass 1: row max
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int cidx = 0; cidx < 128; cidx += 32) {
+                uint32_t v[32];
+                tmem_ld32(tS + lane_off + cidx, v);
+                tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int s = kv0 + cidx + i;
+                        if (s <= row && s >= my_start) mx = fmaxf(mx, __uint_as_float(v[i]));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float m_sub = (m_new == -INFINITY) ? 0.f : m_new * c;
+            const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run * c - m_sub);
+            // pass 2: probabilities -> smem (bf16, swizzled), row sum
+            float rs = 0.f;
+#pragma unroll 1
+            for (int cidx = 0; cidx < 128; cidx += 32) {
+                uint32_t v[32];
+                tmem_ld32(tS + lane_off + cidx, v);
+                tmem_ld_wait();
+                float pv[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float e = exp2f(__uint_as_float(v[i]) * c - m_sub);
+                    if (need_mask) {
+                        const int s = kv0 + cidx + i;
+                        if (!(s <= row && s >= my_start)) e = 0.f;
+                    }
+                    pv[i] = e;
+                    rs += e;
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 u;
+                    u.x = pack_bf16x2(pv[8 * q + 0], pv[8 * q + 1]);
+                    u.y = pack_bf16x2(pv[8 * q + 2], pv[8 * q + 3]);
+                    u.z = pack_bf16x2(pv[8 * q + 4], pv[8 * q + 5]);
+                    u.w = pack_bf16x2(pv[8 * q + 6], pv[8 * q + 7]);
+                    const int chunk = (cidx >> 3) + q;          // 16-byte chunk index 0..15 along kv
+                    const uint32_t off = (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+                    *reinterpret_cast<uint4*>(gP + off) = u;
+                }
+            }
+            l_run = l_run * alpha + rs;
+            m_run = m_new;
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pfull);
+            // fold O_j into the running accumulator
+            ok = mbar_wait(bar_ofull, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int cidx = 0; cidx < HD; cidx += 32) {
+                uint32_t v[32];
+                tmem_ld32(tO + lane_off + cidx, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o_acc[cidx + i] = o_acc[cidx + i] * alpha + __uint_as_float(v[i]);
+            }
+            tc_fence_before();
+        }
+        if (ok && row < p.M) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            __nv_bfloat16* dst = p.O + (long long)row * p.o_stride + head * HD;
+#pragma unroll
+            for (int i = 0; i < HD; i += 8) {
+                uint4 u;
+                u.x = pack_bf16x2(o_acc[i] * inv, o_acc[i + 1] * inv);
+                u.y = pack_bf16x2(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
+                u.z = pack_bf16x2(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
+                u.w = pack_bf16x2(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
+                *reinterpret_cast<uint4*>(dst + i) = u;
+            }
+            p.lse2[(long long)head * p.M + row] = (l_run > 0.f) ? (m_run * c + log2f(l_run)) : -INFINITY;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
+
+template <int HD>
+static int launch_attn_fwd(const CUtensorMap& tm, const AttnFwdParams& p, cudaStream_t st) {
+    using Cfg = AttnFwdCfg<HD>;
+    auto kern = attn_fwd_kernel<HD>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -20;
+        configured = true;
+    }
+    dim3 grid((p.M + 127) / 128, p.H);
+    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(tm, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}
+
+}  // namespace pb
+
+extern "C" int pb_attn_fwd(const void* qkv, const int* seq_start, void* o, float* lse2, int M, int H, int KV, int HD,
+                           long long qkv_stride, long long o_stride, float scale, int* status, void* stream) {
+    using namespace pb;
+    if (HD != 64 && HD != 128) return -1;
+    if (H % KV) return -1;
+    if ((qkv_stride % 8) || (o_stride % 8) || (reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(o) & 15)) return -2;
+    CUtensorMap tm;
+    int rc = make_tmap_bf16_2d(&tm, qkv, uint64_t(H + 2 * KV) * HD, M, qkv_stride, 64, 128);
+    if (rc) return rc;
+    AttnFwdParams p;
+    p.M = M; p.H = H; p.KV = KV; p.seq_start = seq_start; p.O = reinterpret_cast<__nv_bfloat16*>(o); p.o_stride = o_stride;
+    p.lse2 = lse2; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    return HD == 64 ? launch_attn_fwd<64>(tm, p, st) : launch_attn_fwd<128>(tm, p, st);
+}

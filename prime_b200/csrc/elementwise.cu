@@ -1,0 +1,616 @@
+// Bandwidth-bound kernels of the Llama training step for sm_100a: RMSNorm fwd/bwd,
+// RoPE, SwiGLU fwd/bwd, embedding gather / scatter-add, softmax cross-entropy with
+// in-place logit gradient, fused AdamW, and small reductions (sum of squares).
+// All of them move 16-byte vectors, keep fp32 math in registers and use fixed-order
+// reductions so results are bit-reproducible run to run.
+//
+// Reference behaviour being reproduced (paths inside the reference project):
+//   RMSNorm      src/zeroband/models/norms.py:79-106 (eager), :116-221 (Triton fwd/bwd)
+//   RoPE         src/zeroband/models/llama/model.py:118-144 (interleaved complex pairs)
+//   SwiGLU       src/zeroband/models/llama/model.py:340-341
+//   CE / z-loss  src/zeroband/loss.py:70-87 (max-z) and :47-66 (lse^2 z-loss of the fused path)
+//   AdamW        src/zeroband/optimizers.py:25-30 (torch.optim.AdamW semantics)
+#include "common.cuh"
+
+namespace pb {
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+    uint4 u;
+    u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+    u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+// ----------------------------------------------------------------------------
+// RMSNorm forward: one warp per row. y = x * rstd * w ; rstd saved (fp32).
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ w,
+                                                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                          int M, int N, float eps) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    for (long long row = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < M;
+         row += (long long)gridDim.x * warps_per_block) {
+        const __nv_bfloat16* xr = x + row * N;
+        float ss = 0.f;
+        for (int c = lane * 8; c < N; c += 256) {
+            float f[8];
+            load8(xr + c, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+        }
+        ss = warp_sum(ss);
+        const float r = rsqrtf(ss / N + eps);
+        if (lane == 0 && rstd) rstd[row] = r;
+        __nv_bfloat16* yr = y + row * N;
+        for (int c = lane * 8; c < N; c += 256) {
+            float f[8], g[8];
+            load8(xr + c, f);
+            load8(w + c, g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
+            store8(yr + c, f);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------
+// RMSNorm backward. One warp per row; each lane owns columns lane*8 + 256*j.
+//   xhat = x*rstd ; g = dy*w ; dx = (g - xhat * mean(g*xhat)) * rstd (+ dres)
+//   dw  += dy * xhat  (per-CTA partials in fp32, reduced by a second kernel in fixed order)
+// NCH = N / 256 column chunks per lane.
+// ----------------------------------------------------------------------------
+template <int NCH>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ w,
+                                                          const float* __restrict__ rstd,
+                                                          const __nv_bfloat16* __restrict__ dy,
+                                                          const __nv_bfloat16* __restrict__ dres,
+                                                          __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial,
+                                                          int M) {
+    constexpr int N = NCH * 256;
+    __shared__ float red[8][32 * 8 + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps_per_block = blockDim.x >> 5;
+    float wv[NCH][8];
+    float dwacc[NCH][8];
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+        load8(w + j * 256 + lane * 8, wv[j]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+    }
+    for (long long row = (long long)blockIdx.x * warps_per_block + warp; row < M;
+         row += (long long)gridDim.x * warps_per_block) {
+        const float r = rstd[row];
+        float xh[NCH][8], g[NCH][8];
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+            float dyv[8];
+            load8(x + row * N + j * 256 + lane * 8, xh[j]);
+            load8(dy + row * N + j * 256 + lane * 8, dyv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                xh[j][i] *= r;
+                g[j][i] = dyv[i] * wv[j][i];
+                dot += g[j][i] * xh[j][i];
+                dwacc[j][i] += dyv[i] * xh[j][i];
+            }
+        }
+        dot = warp_sum(dot) * (1.f / N);
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = (g[j][i] - xh[j][i] * dot) * r;
+            if (dres) {
+                float dr[8];
+                load8(dres + row * N + j * 256 + lane * 8, dr);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] += dr[i];
+            }
+            store8(dx + row * N + j * 256 + lane * 8, o);
+        }
+    }
+    // fixed-order reduction of the per-warp dw accumulators across the CTA
+    for (int j = 0; j < NCH; ++j) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) red[warp][lane * 8 + i] = dwacc[j][i];
+        __syncthreads();
+        if (warp == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float s = 0.f;
+                for (int ww = 0; ww < warps_per_block; ++ww) s += red[ww][lane * 8 + i];
+                dw_partial[(long long)blockIdx.x * N + j * 256 + lane * 8 + i] = s;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// dw[c] (+)= sum_b partial[b, c]  (fixed order); output bf16 or fp32
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, void* __restrict__ out, int nb, int N,
+                                       int out_fp32, int accumulate) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= N) return;
+    float s = 0.f;
+    for (int b = 0; b < nb; ++b) s += partial[(long long)b * N + c];
+    if (out_fp32) {
+        float* o = reinterpret_cast<float*>(out);
+        o[c] = accumulate ? o[c] + s : s;
+    } else {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+        o[c] = __float2bfloat16(accumulate ? __bfloat162float(o[c]) + s : s);
+    }
+}
+
+// ----------------------------------------------------------------------------
+// RoPE on interleaved (re, im) pairs, in place, on the q and k slices of a fused
+// qkv activation [M, (H + 2*KV) * hd]. Position of row m is m % T.
+// table: [>=T, hd/2, 2] fp32 (cos, sin). sign=+1 forward, -1 backward (conjugate).
+// ----------------------------------------------------------------------------
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ table, long long M, int T,
+                            int n_rot_heads, int hd, int row_stride, float sign) {
+    // one thread handles 8 consecutive elements (4 pairs)
+    const int vec_per_head = hd / 8;
+    const long long total = M * n_rot_heads * vec_per_head;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int v = int(i % vec_per_head);
+        const long long t = i / vec_per_head;
+        const int h = int(t % n_rot_heads);
+        const long long m = t / n_rot_heads;
+        const int pos = int(m % T);
+        __nv_bfloat16* p = qkv + m * row_stride + h * hd + v * 8;
+        float f[8];
+        load8(p, f);
+        const float4* cs = reinterpret_cast<const float4*>(table + ((long long)pos * (hd / 2) + v * 4) * 2);
+        float4 c0 = cs[0], c1 = cs[1];
+        const float co[4] = {c0.x, c0.z, c1.x, c1.z};
+        const float si[4] = {c0.y * sign, c0.w * sign, c1.y * sign, c1.w * sign};
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            o[2 * k] = f[2 * k] * co[k] - f[2 * k + 1] * si[k];
+            o[2 * k + 1] = f[2 * k] * si[k] + f[2 * k + 1] * co[k];
+        }
+        store8(p, o);
+    }
+}
+
+// ----------------------------------------------------------------------------
+// SwiGLU. h13 is [M, 2F]: gate = cols [0,F), up = cols [F,2F). act = silu(gate)*up.
+// ----------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ h13, __nv_bfloat16* __restrict__ act,
+                                  long long M, int F) {
+    const int vpr = F / 8;
+    const long long total = M * vpr;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / vpr;
+        const int c = int(i % vpr) * 8;
+        float g[8], u[8], o[8];
+        load8(h13 + m * 2 * F + c, g);
+        load8(h13 + m * 2 * F + F + c, u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+        store8(act + m * F + c, o);
+    }
+}
+// dgate = dact * up * sig*(1 + g*(1-sig)) ; dup = dact * silu(g). Written into dh13 [M,2F]
+// (dh13 may alias h13: each thread reads its inputs before writing the same locations).
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* h13, const __nv_bfloat16* __restrict__ dact,
+                                  __nv_bfloat16* dh13, long long M, int F) {
+    const int vpr = F / 8;
+    const long long total = M * vpr;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / vpr;
+        const int c = int(i % vpr) * 8;
+        float g[8], u[8], d[8], dg[8], du[8];
+        load8(h13 + m * 2 * F + c, g);
+        load8(h13 + m * 2 * F + F + c, u);
+        load8(dact + m * F + c, d);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float s = 1.f / (1.f + __expf(-g[k]));
+            du[k] = d[k] * g[k] * s;
+            dg[k] = d[k] * u[k] * s * (1.f + g[k] * (1.f - s));
+        }
+        store8(dh13 + m * 2 * F + c, dg);
+        store8(dh13 + m * 2 * F + F + c, du);
+    }
+}
+
+// ----------------------------------------------------------------------------
+// Embedding gather and its backward (scatter-add with atomics; fp32 or bf16 grads)
+// ----------------------------------------------------------------------------
+__global__ void embedding_fwd_kernel(const long long* __restrict__ tok, const __nv_bfloat16* __restrict__ E,
+                                     __nv_bfloat16* __restrict__ out, long long M, int D) {
+    const int vpr = D / 8;
+    const long long total = M * vpr;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / vpr;
+        const int c = int(i % vpr) * 8;
+        *reinterpret_cast<uint4*>(out + m * D + c) = *reinterpret_cast<const uint4*>(E + tok[m] * D + c);
+    }
+}
+__global__ void embedding_bwd_kernel(const long long* __restrict__ tok, const __nv_bfloat16* __restrict__ dout,
+                                     void* __restrict__ dE, long long M, int D, int grad_fp32) {
+    const int vpr = D / 8;
+    const long long total = M * vpr;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / vpr;
+        const int c = int(i % vpr) * 8;
+        const long long t = tok[m];
+        if (grad_fp32) {
+            float f[8];
+            load8(dout + m * D + c, f);
+            float* g = reinterpret_cast<float*>(dE) + t * D + c;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) atomicAdd(g + k, f[k]);
+        } else {
+            uint4 u = *reinterpret_cast<const uint4*>(dout + m * D + c);
+            __nv_bfloat162* g = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(dE) + t * D + c);
+            atomicAdd(g + 0, *reinterpret_cast<__nv_bfloat162*>(&u.x));
+            atomicAdd(g + 1, *reinterpret_cast<__nv_bfloat162*>(&u.y));
+            atomicAdd(g + 2, *reinterpret_cast<__nv_bfloat162*>(&u.z));
+            atomicAdd(g + 3, *reinterpret_cast<__nv_bfloat162*>(&u.w));
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------
+// Cross-entropy over bf16 logits [rows, V] (row pitch ld) with in-place gradient.
+// One CTA per row; online max/sum in pass 1, gradient written in pass 2 (row is
+// L2-resident). Per-row outputs: loss_i (0 for ignored rows) and z_i.
+//   z_mode 0: none; 1: max-z  (z_i = max^2);  2: lse^2 (z_i = lse^2)
+//   dlogits = scale * [softmax - onehot] + dz, scale = *inv_count * grad_scale
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(512) cross_entropy_kernel(__nv_bfloat16* logits, const long long* __restrict__ labels,
+                                                            float* __restrict__ loss_rows, float* __restrict__ z_rows,
+                                                            const float* __restrict__ inv_count, float grad_scale,
+                                                            int V, long long ld, int ignore_index, int z_mode,
+                                                            float z_weight, int write_grad) {
+    __shared__ float s_m[16], s_s[16];
+    __shared__ int s_arg[16];
+    const long long row = blockIdx.x;
+    __nv_bfloat16* lr = logits + row * ld;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const long long label = labels[row];
+    const bool ignored = (label == ignore_index);
+    float mx = -INFINITY, sm = 0.f;
+    int arg = 0;
+    const int V8 = V & ~7;
+    for (int c = tid * 8; c < V8; c += blockDim.x * 8) {
+        float f[8];
+        load8(lr + c, f);
+        float cm = f[0];
+        int ca = 0;
+#pragma unroll
+        for (int k = 1; k < 8; ++k)
+            if (f[k] > cm) { cm = f[k]; ca = k; }
+        if (cm > mx) {
+            sm *= __expf(mx - cm);
+            mx = cm;
+            arg = c + ca;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sm += __expf(f[k] - mx);
+    }
+    for (int c = V8 + tid; c < V; c += blockDim.x) {
+        const float f = __bfloat162float(lr[c]);
+        if (f > mx) { sm *= __expf(mx - f); mx = f; arg = c; }
+        sm += __expf(f - mx);
+    }
+    // warp then CTA reduction of (max, sum, argmax); ties resolve to the lowest index
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+        const float os = __shfl_xor_sync(0xffffffffu, sm, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        const float nm = fmaxf(mx, om);
+        sm = (mx == -INFINITY ? 0.f : sm * __expf(mx - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+        if (om > mx || (om == mx && oa < arg)) arg = oa;
+        mx = nm;
+    }
+    if (lane == 0) { s_m[warp] = mx; s_s[warp] = sm; s_arg[warp] = arg; }
+    __syncthreads();
+    mx = s_m[0]; sm = s_s[0]; arg = s_arg[0];
+    for (int w2 = 1; w2 < nwarps; ++w2) {
+        const float om = s_m[w2], os = s_s[w2];
+        const int oa = s_arg[w2];
+        const float nm = fmaxf(mx, om);
+        sm = (mx == -INFINITY ? 0.f : sm * __expf(mx - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+        if (om > mx || (om == mx && oa < arg)) arg = oa;
+        mx = nm;
+    }
+    const float lse = mx + __logf(sm);
+    if (tid == 0) {
+        float li = 0.f, zi = 0.f;
+        if (!ignored) {
+            li = lse - __bfloat162float(lr[label]);
+            zi = z_mode == 1 ? mx * mx : (z_mode == 2 ? lse * lse : 0.f);
+        }
+        loss_rows[row] = li;
+        if (z_rows) z_rows[row] = zi;
+    }
+    if (!write_grad) return;
+    __syncthreads();  // label logit was read above before anyone overwrites it
+    const float scale = ignored ? 0.f : (*inv_count) * grad_scale;
+    // d(lse^2 * zw)/dlogit = 2 zw lse softmax ;  d(max^2 * zw)/dlogit = 2 zw max at argmax
+    const float soft_coef = scale * (1.f + (z_mode == 2 ? 2.f * z_weight * lse : 0.f));
+    const float max_coef = (z_mode == 1) ? scale * 2.f * z_weight * mx : 0.f;
+    for (int c = tid * 8; c < V8; c += blockDim.x * 8) {
+        float f[8];
+        load8(lr + c, f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float g = soft_coef * __expf(f[k] - lse);
+            if (c + k == label) g -= scale;
+            if (c + k == arg) g += max_coef;
+            f[k] = g;
+        }
+        store8(lr + c, f);
+    }
+    for (int c = V8 + tid; c < V; c += blockDim.x) {
+        float g = soft_coef * __expf(__bfloat162float(lr[c]) - lse);
+        if (c == label) g -= scale;
+        if (c == arg) g += max_coef;
+        lr[c] = __float2bfloat16(g);
+    }
+}
+
+// count of labels != ignore_index -> inv_count = 1/max(count,1) ; single CTA, fixed order
+__global__ void count_valid_kernel(const long long* __restrict__ labels, long long n, int ignore_index,
+                                   float* __restrict__ inv_count) {
+    __shared__ long long s[32];
+    long long c = 0;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) c += (labels[i] != ignore_index);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        long long t = 0;
+        for (int i = 0; i < (blockDim.x >> 5); ++i) t += s[i];
+        inv_count[0] = 1.f / float(t > 0 ? t : 1);
+        inv_count[1] = float(t);
+    }
+}
+
+// out[0] (+)= scale * sum(x[0:n]) — two-stage fixed-order sum of fp32 values
+__global__ void sum_stage1_kernel(const float* __restrict__ x, long long n, float* __restrict__ partial) {
+    __shared__ float s[32];
+    float a = 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        a += x[i];
+    a = warp_sum(a);
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = a;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < (blockDim.x >> 5); ++i) t += s[i];
+        partial[blockIdx.x] = t;
+    }
+}
+__global__ void sum_stage2_kernel(const float* __restrict__ partial, int nb, const float* __restrict__ scale_ptr,
+                                  float scale, float* __restrict__ out, int accumulate) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < nb; ++i) t += partial[i];
+        t *= scale * (scale_ptr ? *scale_ptr : 1.f);
+        out[0] = accumulate ? out[0] + t : t;
+    }
+}
+
+// ----------------------------------------------------------------------------
+// sum of squares of a bf16 / fp32 buffer -> per-CTA partials (fixed order)
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ partial) {
+    __shared__ float s[32];
+    float a = 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float f = float(x[i]);
+        a += f * f;
+    }
+    a = warp_sum(a);
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = a;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < (blockDim.x >> 5); ++i) t += s[i];
+        partial[blockIdx.x] = t;
+    }
+}
+
+// ----------------------------------------------------------------------------
+// AdamW on a flat fp32 shard with bf16 or fp32 gradients; refreshes the bf16 compute copy.
+//   clip: optional device pointer to the total grad norm; grads are scaled by
+//         min(1, max_norm / (norm + 1e-6)) as torch.nn.utils.clip_grad_norm_ does.
+// ----------------------------------------------------------------------------
+template <typename G>
+__global__ void adamw_kernel(float* __restrict__ p, const G* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                             __nv_bfloat16* __restrict__ p_bf16, long long n, float lr, float beta1, float beta2,
+                             float eps, float wd, float bc1, float bc2, const float* __restrict__ gnorm,
+                             float max_norm, float gscale) {
+    float clip = gscale;
+    if (gnorm) {
+        const float c = max_norm / (*gnorm + 1e-6f);
+        clip *= c < 1.f ? c : 1.f;
+    }
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float gi = float(g[i]) * clip;
+        float pi = p[i];
+        pi *= (1.f - lr * wd);
+        const float mi = beta1 * m[i] + (1.f - beta1) * gi;
+        const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        const float denom = sqrtf(vi) / bc2 + eps;   // bc2 = sqrt(1 - beta2^t)
+        pi -= (lr / bc1) * (mi / denom);
+        p[i] = pi;
+        if (p_bf16) p_bf16[i] = __float2bfloat16(pi);
+    }
+}
+
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = __float2bfloat16(src[i]);
+}
+
+// residual add: out = a + b (bf16)
+__global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                __nv_bfloat16* __restrict__ out, long long n8) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+        float x[8], y[8];
+        load8(a + i * 8, x);
+        load8(b + i * 8, y);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x[k] += y[k];
+        store8(out + i * 8, x);
+    }
+}
+
+static inline int grid_for(long long work_items, int block, int max_blocks = 148 * 8) {
+    long long b = (work_items + block - 1) / block;
+    if (b < 1) b = 1;
+    return int(b < max_blocks ? b : max_blocks);
+}
+
+}  // namespace pb
+
+using namespace pb;
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+#define CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : -30)
+
+extern "C" int pb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int M, int N, float eps, void* stream) {
+    if (N % 8) return -1;
+    rmsnorm_fwd_kernel<<<grid_for(M, 8), 256, 0, ST(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                                (__nv_bfloat16*)y, rstd, M, N, eps);
+    return CHECK_LAUNCH();
+}
+
+// number of CTAs (= rows of the fp32 partial buffer [ctas, N]) the backward uses
+extern "C" int pb_rmsnorm_bwd_ctas() { return 148 * 2; }
+
+extern "C" int pb_rmsnorm_bwd(const void* x, const void* w, const float* rstd, const void* dy, const void* dres,
+                              void* dx, float* dw_partial, void* dw, int dw_fp32, int dw_accumulate, int M, int N,
+                              void* stream) {
+    if (N % 256 || N > 4096) return -1;
+    const int ctas = pb_rmsnorm_bwd_ctas();
+    auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w; auto DY = (const __nv_bfloat16*)dy;
+    auto DR = (const __nv_bfloat16*)dres; auto DX = (__nv_bfloat16*)dx;
+#define RB(NCH) case NCH: rmsnorm_bwd_kernel<NCH><<<ctas, 256, 0, ST(stream)>>>(X, W, rstd, DY, DR, DX, dw_partial, M); break;
+    switch (N / 256) {
+        RB(1) RB(2) RB(3) RB(4) RB(6) RB(8) RB(12) RB(16)
+        default: return -1;
+    }
+#undef RB
+    if (cudaGetLastError() != cudaSuccess) return -30;
+    colsum_partials_kernel<<<(N + 255) / 256, 256, 0, ST(stream)>>>(dw_partial, dw, ctas, N, dw_fp32, dw_accumulate);
+    return CHECK_LAUNCH();
+}
+
+extern "C" int pb_rope(void* qkv, const float* table, long long M, int T, int n_rot_heads, int hd, int row_stride,
+                       int backward, void* stream) {
+    if (hd % 8 || row_stride % 8) return -1;
+    rope_kernel<<<grid_for(M * n_rot_heads * (hd / 8), 256), 256, 0, ST(stream)>>>(
+        (__nv_bfloat16*)qkv, table, M, T, n_rot_heads, hd, row_stride, backward ? -1.f : 1.f);
+    return CHECK_LAUNCH();
+}
+
+extern "C" int pb_swiglu_fwd(const void* h13, void* act, long long M, int F, void* stream) {
+    if (F % 8) return -1;
+    swiglu_fwd_kernel<<<grid_for(M * (F / 8), 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)h13, (__nv_bfloat16*)act, M, F);
+    return CHECK_LAUNCH();
+}
+extern "C" int pb_swiglu_bwd(const void* h13, const void* dact, void* dh13, long long M, int F, void* stream) {
+    if (F % 8) return -1;
+    swiglu_bwd_kernel<<<grid_for(M * (F / 8), 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)h13, (const __nv_bfloat16*)dact,
+                                                                          (__nv_bfloat16*)dh13, M, F);
+    return CHECK_LAUNCH();
+}
+
+extern "C" int pb_embedding_fwd(const long long* tok, const void* E, void* out, long long M, int D, void* stream) {
+    if (D % 8) return -1;
+    embedding_fwd_kernel<<<grid_for(M * (D / 8), 256), 256, 0, ST(stream)>>>(tok, (const __nv_bfloat16*)E, (__nv_bfloat16*)out, M, D);
+    return CHECK_LAUNCH();
+}
+extern "C" int pb_embedding_bwd(const long long* tok, const void* dout, void* dE, long long M, int D, int grad_fp32, void* stream) {
+    if (D % 8) return -1;
+    embedding_bwd_kernel<<<grid_for(M * (D / 8), 256), 256, 0, ST(stream)>>>(tok, (const __nv_bfloat16*)dout, dE, M, D, grad_fp32);
+    return CHECK_LAUNCH();
+}
+
+extern "C" int pb_count_valid(const long long* labels, long long n, int ignore_index, float* inv_count, void* stream) {
+    count_valid_kernel<<<1, 1024, 0, ST(stream)>>>(labels, n, ignore_index, inv_count);
+    return CHECK_LAUNCH();
+}
+
+extern "C" int pb_cross_entropy(void* logits, const long long* labels, float* loss_rows, float* z_rows,
+                                const float* inv_count, float grad_scale, long long rows, int V, long long ld,
+                                int ignore_index, int z_mode, float z_weight, int write_grad, void* stream) {
+    if (rows <= 0) return 0;
+    if (ld % 8) return -1;
+    cross_entropy_kernel<<<(unsigned)rows, 512, 0, ST(stream)>>>((__nv_bfloat16*)logits, labels, loss_rows, z_rows, inv_count,
+                                                                 grad_scale, V, ld, ignore_index, z_mode, z_weight, write_grad);
+    return CHECK_LAUNCH();
+}
+
+// out (+)= scale * (*scale_ptr) * sum(x) ; scratch: >= 1024 floats
+extern "C" int pb_sum_f32(const float* x, long long n, float* scratch, const float* scale_ptr, float scale, float* out,
+                          int accumulate, void* stream) {
+    const int nb = grid_for(n, 256, 1024);
+    sum_stage1_kernel<<<nb, 256, 0, ST(stream)>>>(x, n, scratch);
+    sum_stage2_kernel<<<1, 32, 0, ST(stream)>>>(scratch, nb, scale_ptr, scale, out, accumulate);
+    return CHECK_LAUNCH();
+}
+
+// out (+)= sum(x^2) ; scratch >= 1024 floats
+extern "C" int pb_sumsq(const void* x, long long n, int is_fp32, float* scratch, float* out, int accumulate, void* stream) {
+    const int nb = grid_for(n, 256, 1024);
+    if (is_fp32) sumsq_kernel<float><<<nb, 256, 0, ST(stream)>>>((const float*)x, n, scratch);
+    else sumsq_kernel<__nv_bfloat16><<<nb, 256, 0, ST(stream)>>>((const __nv_bfloat16*)x, n, scratch);
+    sum_stage2_kernel<<<1, 32, 0, ST(stream)>>>(scratch, nb, nullptr, 1.f, out, accumulate);
+    return CHECK_LAUNCH();
+}
+
+extern "C" int pb_adamw(float* p, const void* g, int g_fp32, float* m, float* v, void* p_bf16, long long n, float lr,
+                        float beta1, float beta2, float eps, float wd, int step, const float* gnorm, float max_norm,
+                        float gscale, void* stream) {
+    if (n <= 0) return 0;
+    const float bc1 = 1.f - powf(beta1, float(step));
+    const float bc2 = sqrtf(1.f - powf(beta2, float(step)));
+    const int nb = grid_for(n, 256, 148 * 16);
+    if (g_fp32)
+        adamw_kernel<float><<<nb, 256, 0, ST(stream)>>>(p, (const float*)g, m, v, (__nv_bfloat16*)p_bf16, n, lr, beta1, beta2, eps,
+                                                         wd, bc1, bc2, gnorm, max_norm, gscale);
+    else
+        adamw_kernel<__nv_bfloat16><<<nb, 256, 0, ST(stream)>>>(p, (const __nv_bfloat16*)g, m, v, (__nv_bfloat16*)p_bf16, n, lr,
+                                                                 beta1, beta2, eps, wd, bc1, bc2, gnorm, max_norm, gscale);
+    return CHECK_LAUNCH();
+}
+
+extern "C" int pb_cast_f32_bf16(const float* src, void* dst, long long n, void* stream) {
+    if (n <= 0) return 0;
+    cast_f32_to_bf16_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, ST(stream)>>>(src, (__nv_bfloat16*)dst, n);
+    return CHECK_LAUNCH();
+}
+
+extern "C" int pb_add_bf16(const void* a, const void* b, void* out, long long n, void* stream) {
+    if (n % 8) return -1;
+    add_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, n / 8);
+    return CHECK_LAUNCH();
+}
