@@ -1,0 +1,472 @@
+// Flash attention backward (causal / document mask, GQA) for sm_100a on tcgen05 + TMEM + TMA.
+//
+// One CTA owns one 128-row KV tile of one KV head and walks every (query head of the group,
+// query tile) pair that can see it. Per pair (all MMAs are 128-row tcgen05 instructions):
+//   S  = Q K^T,  dP = dO V^T                 -> TMEM
+//   P  = exp2(S*c - lse2),  dS = P * (dP - D) -> bf16 in shared memory (softmax warps)
+//   dV += P^T dO,  dK += dS^T Q               -> TMEM accumulators kept for the whole CTA
+//   dQ  = dS K                                -> TMEM -> fp32 red.global.add into dq_acc
+// D[h, m] = rowsum(dO * O) comes from a small pre-pass. dK/dV of a KV head are reduced over the
+// query heads of its group inside the CTA (no repeat_kv materialisation, no cross-CTA atomics
+// for them). The same shared-memory tile is consumed K-major by one MMA and MN-major by another
+// (e.g. Q is A of S and B of dK), which the 128-byte-swizzled layout allows without a copy.
+// Gradient semantics match autograd through the reference attention
+// (models/llama/model.py:282-302) for scores scaled by `scale`.
+#include "common.cuh"
+
+namespace pb {
+
+struct AttnBwdParams {
+    int M, H, KV, n_tiles;
+    const int* seq_start;
+    const float* lse2;     // [H, M]
+    const float* D;        // [H, M]
+    float* dq_acc;         // [M, H*HD] fp32, zero-initialised by the caller
+    __nv_bfloat16* dqkv;   // [M, (H+2KV)*HD]; this kernel writes the k and v column blocks
+    long long dqkv_stride;
+    float scale, scale_log2;
+    int* status;
+};
+
+template <int HD>
+struct AttnBwdCfg {
+    static constexpr int TILE_BYTES = 128 * HD * 2;
+    static constexpr int PS_BYTES = 128 * 128 * 2;
+    static constexpr int STAGES = (HD == 64) ? 2 : 1;
+    static constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * STAGES) + 2 * PS_BYTES + 1024 + 256;
+    static constexpr int T_S = 0, T_DP = 128;
+    static constexpr int T_DV = 256, T_DK = 256 + HD;
+    static constexpr int T_DQ = (HD == 64) ? 384 : 0;   // HD=128: dQ reuses the S columns
+    static constexpr bool DQ_ALIASES_S = (HD != 64);
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+                const AttnBwdParams p) {
+    using Cfg = AttnBwdCfg<HD>;
+    constexpr int NB = HD / 64;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sK = base;
+    const uint32_t sV = sK + Cfg::TILE_BYTES;
+    const uint32_t sQ = sV + Cfg::TILE_BYTES;                    // [STAGES]
+    const uint32_t sDO = sQ + STAGES * Cfg::TILE_BYTES;          // [STAGES]
+    const uint32_t sP = sDO + STAGES * Cfg::TILE_BYTES;
+    const uint32_t sDS = sP + Cfg::PS_BYTES;
+    uint8_t* gP = gen + (sP - base);
+    uint8_t* gDS = gen + (sDS - base);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gen + (sDS - base) + Cfg::PS_BYTES);
+    const uint32_t bar_kv = smem_u32(bars);
+    const uint32_t bar_qfull = bar_kv + 8;         // [2]
+    const uint32_t bar_dofull = bar_qfull + 16;    // [2]
+    const uint32_t bar_qdoempty = bar_dofull + 16; // [2]
+    const uint32_t bar_sfull = bar_qdoempty + 16;
+    const uint32_t bar_dpfull = bar_sfull + 8;
+    const uint32_t bar_pdsfull = bar_dpfull + 8;
+    const uint32_t bar_dqfull = bar_pdsfull + 8;
+    const uint32_t bar_dqempty = bar_dqfull + 8;
+    const uint32_t bar_final = bar_dqempty + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kv_tile = blockIdx.x;
+    const int g = blockIdx.y;
+    const int G = p.H / p.KV;
+    const int kv0 = kv_tile * 128;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_kv, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar_qfull + 8 * s, 1);
+            mbar_init(bar_dofull + 8 * s, 1);
+            mbar_init(bar_qdoempty + 8 * s, 1);
+        }
+        mbar_init(bar_sfull, 1);
+        mbar_init(bar_dpfull, 1);
+        mbar_init(bar_pdsfull, 4);
+        mbar_init(bar_dqfull, 1);
+        mbar_init(bar_dqempty, 4);
+        mbar_init(bar_final, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQKV);
+        tma_prefetch_desc(&tmDO);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // query tiles that can see this kv tile: from the diagonal up to the last tile whose first
+    // row's sequence starts at or before the last kv row (seq_start is non-decreasing).
+    int i_hi = kv_tile;
+    while (i_hi + 1 < p.n_tiles && p.seq_start[(i_hi + 1) * 128] <= kv0 + 127) ++i_hi;
+    const int n_q = i_hi - kv_tile + 1;
+    const int n_it = n_q * G;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(bar_kv, 2 * Cfg::TILE_BYTES);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                tma_load_2d(sK + b * 16384, &tmQKV, bar_kv, (p.H + g) * HD + 64 * b, kv0);
+                tma_load_2d(sV + b * 16384, &tmQKV, bar_kv, (p.H + p.KV + g) * HD + 64 * b, kv0);
+            }
+        }
+        bool ok = true;
+        for (int it = 0; it < n_it && ok; ++it) {
+            const int st = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            ok = mbar_wait(bar_qdoempty + 8 * st, ph ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (lane == 0) {
+                const int hq = g * G + it / n_q;
+                const int q0 = (kv_tile + it % n_q) * 128;
+                mbar_expect_tx(bar_qfull + 8 * st, Cfg::TILE_BYTES);
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                    tma_load_2d(sQ + st * Cfg::TILE_BYTES + b * 16384, &tmQKV, bar_qfull + 8 * st, hq * HD + 64 * b, q0);
+                mbar_expect_tx(bar_dofull + 8 * st, Cfg::TILE_BYTES);
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                    tma_load_2d(sDO + st * Cfg::TILE_BYTES + b * 16384, &tmDO, bar_dofull + 8 * st, hq * HD + 64 * b, q0);
+            }
+            __syncwarp();
+        }
+        if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(10000);
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_kv = umma_idesc_bf16(128, HD, 1, 1);   // dV, dK: both operands MN-major
+        constexpr uint32_t idesc_dq = umma_idesc_bf16(128, HD, 0, 1);
+        const uint32_t tS = tmem_base + Cfg::T_S, tDP = tmem_base + Cfg::T_DP, tDV = tmem_base + Cfg::T_DV,
+                       tDK = tmem_base + Cfg::T_DK, tDQ = tmem_base + Cfg::T_DQ;
+        auto issue_s_dp = [&](int st, bool& ok, int it) {
+            const uint32_t ph = (it / STAGES) & 1;
+            ok = mbar_wait(bar_qfull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            if (Cfg::DQ_ALIASES_S && it > 0) {
+                ok = mbar_wait(bar_dqempty, (it - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) return;
+            }
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t q = sQ + st * Cfg::TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+                    umma_f16_ss(tS, umma_smem_desc(q + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024), idesc_s, k ? 1u : 0u);
+                }
+                umma_commit(bar_sfull);
+            }
+            __syncwarp();
+            ok = mbar_wait(bar_dofull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t d = sDO + st * Cfg::TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+                    umma_f16_ss(tDP, umma_smem_desc(d + off, 16, 1024), umma_smem_desc(sV + off, 16, 1024), idesc_s, k ? 1u : 0u);
+                }
+                umma_commit(bar_dpfull);
+            }
+            __syncwarp();
+        };
+        bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok && n_it > 0) issue_s_dp(0, ok, 0);
+        for (int it = 0; it < n_it && ok; ++it) {
+            const int st = it % STAGES;
+            ok = mbar_wait(bar_pdsfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t q = sQ + st * Cfg::TILE_BYTES, d = sDO + st * Cfg::TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < 8; ++k)   // reduction over the 128 query rows
+                    umma_f16_ss(tDV, umma_smem_desc(sP + k * 2048, 16384, 1024), umma_smem_desc(d + k * 2048, 16384, 1024),
+                                idesc_kv, (it | k) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    umma_f16_ss(tDK, umma_smem_desc(sDS + k * 2048, 16384, 1024), umma_smem_desc(q + k * 2048, 16384, 1024),
+                                idesc_kv, (it | k) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)   // reduction over the 128 kv rows
+                    umma_f16_ss(tDQ, umma_smem_desc(sDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                                umma_smem_desc(sK + k * 2048, 16384, 1024), idesc_dq, k ? 1u : 0u);
+                umma_commit(bar_dqfull);
+                umma_commit(bar_qdoempty + 8 * st);
+                if (it == n_it - 1) umma_commit(bar_final);
+            }
+            __syncwarp();
+            if (it + 1 < n_it) issue_s_dp((it + 1) % STAGES, ok, it + 1);
+        }
+    } else {
+        // ------------------------------ softmax / dS / epilogue warps ------------------------------
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const uint32_t lane_off = uint32_t(quad * 32) << 16;
+        const uint32_t tS = tmem_base + Cfg::T_S + lane_off, tDP = tmem_base + Cfg::T_DP + lane_off,
+                       tDV = tmem_base + Cfg::T_DV + lane_off, tDK = tmem_base + Cfg::T_DK + lane_off,
+                       tDQ = tmem_base + Cfg::T_DQ + lane_off;
+        const float c = p.scale_log2;
+        bool ok = true;
+        for (int it = 0; it < n_it && ok; ++it) {
+            const int hq = g * G + it / n_q;
+            const int q0 = (kv_tile + it % n_q) * 128;
+            const int row = q0 + r;
+            const bool row_ok = row < p.M;
+            const float lse = row_ok ? p.lse2[(long long)hq * p.M + row] : 0.f;
+            const float Dr = row_ok ? p.D[(long long)hq * p.M + row] : 0.f;
+            const int my_start = row_ok ? p.seq_start[row] : 0;
+            const int tile_last_start = p.seq_start[min(q0 + 127, p.M - 1)];
+            const bool need_mask = (kv0 + 127 > q0) || (kv0 < tile_last_start) || (q0 + 127 >= p.M);
+            ok = mbar_wait(bar_sfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ok = mbar_wait(bar_dpfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int cidx = 0; cidx < 128; cidx += 32) {
+                uint32_t sv[32], dv[32];
+                tmem_ld32(tS + cidx, sv);
+                tmem_ld32(tDP + cidx, dv);
+                tmem_ld_wait();
+                float pv[32], ds[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float e = exp2f(__uint_as_float(sv[i]) * c - lse);
+                    if (need_mask) {
+                        const int s = kv0 + cidx + i;
+                        if (!(row_ok && s <= row && s >= my_start)) e = 0.f;
+                    }
+                    pv[i] = e;
+                    ds[i] = e * (__uint_as_float(dv[i]) - Dr);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 u, w;
+                    u.x = pack_bf16x2(pv[8 * q + 0], pv[8 * q + 1]); u.y = pack_bf16x2(pv[8 * q + 2], pv[8 * q + 3]);
+                    u.z = pack_bf16x2(pv[8 * q + 4], pv[8 * q + 5]); u.w = pack_bf16x2(pv[8 * q + 6], pv[8 * q + 7]);
+                    w.x = pack_bf16x2(ds[8 * q + 0], ds[8 * q + 1]); w.y = pack_bf16x2(ds[8 * q + 2], ds[8 * q + 3]);
+                    w.z = pack_bf16x2(ds[8 * q + 4], ds[8 * q + 5]); w.w = pack_bf16x2(ds[8 * q + 6], ds[8 * q + 7]);
+                    const int chunk = (cidx >> 3) + q;
+                    const uint32_t off = (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+                    *reinterpret_cast<uint4*>(gP + off) = u;
+                    *reinterpret_cast<uint4*>(gDS + off) = w;
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pdsfull);
+            // dQ tile -> global fp32 accumulator
+            ok = mbar_wait(bar_dqfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            float* dq_row = p.dq_acc + (long long)row * (p.H * HD) + hq * HD;
+#pragma unroll 1
+            for (int cidx = 0; cidx < HD; cidx += 32) {
+                uint32_t v[32];
+                tmem_ld32(tDQ + cidx, v);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        red_add_v4(dq_row + cidx + i, __uint_as_float(v[i]) * p.scale, __uint_as_float(v[i + 1]) * p.scale,
+                                   __uint_as_float(v[i + 2]) * p.scale, __uint_as_float(v[i + 3]) * p.scale);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_dqempty);
+        }
+        // final: dK (scaled) and dV of this kv tile -> bf16 gradient buffer
+        if (ok && n_it > 0) {
+            ok = mbar_wait(bar_final, 0, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            const int row = kv0 + r;
+            __nv_bfloat16* dk_row = p.dqkv + (long long)row * p.dqkv_stride + (p.H + g) * HD;
+            __nv_bfloat16* dv_row = p.dqkv + (long long)row * p.dqkv_stride + (p.H + p.KV + g) * HD;
+#pragma unroll 1
+            for (int cidx = 0; cidx < HD; cidx += 32) {
+                uint32_t a[32], b[32];
+                if (n_it > 0) {
+                    tmem_ld32(tDK + cidx, a);
+                    tmem_ld32(tDV + cidx, b);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) { a[i] = 0; b[i] = 0; }
+                }
+                if (row < p.M) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 u, w;
+                        u.x = pack_bf16x2(__uint_as_float(a[i]) * p.scale, __uint_as_float(a[i + 1]) * p.scale);
+                        u.y = pack_bf16x2(__uint_as_float(a[i + 2]) * p.scale, __uint_as_float(a[i + 3]) * p.scale);
+                        u.z = pack_bf16x2(__uint_as_float(a[i + 4]) * p.scale, __uint_as_float(a[i + 5]) * p.scale);
+                        u.w = pack_bf16x2(__uint_as_float(a[i + 6]) * p.scale, __uint_as_float(a[i + 7]) * p.scale);
+                        w.x = pack_bf16x2(__uint_as_float(b[i]), __uint_as_float(b[i + 1]));
+                        w.y = pack_bf16x2(__uint_as_float(b[i + 2]), __uint_as_float(b[i + 3]));
+                        w.z = pack_bf16x2(__uint_as_float(b[i + 4]), __uint_as_float(b[i + 5]));
+                        w.w = pack_bf16x2(__uint_as_float(b[i + 6]), __uint_as_float(b[i + 7]));
+                        *reinterpret_cast<uint4*>(dk_row + cidx + i) = u;
+                        *reinterpret_cast<uint4*>(dv_row + cidx + i) = w;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// D[h, m] = sum_d dO[m, h*HD + d] * O[m, h*HD + d]; one warp per (m, h)
+__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                     float* __restrict__ D, int M, int H, int HD, long long o_stride, long long do_stride) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (long long)M * H) return;
+    const int h = int(wid % H);
+    const long long m = wid / H;
+    float acc = 0.f;
+    for (int d = lane * 2; d < HD; d += 64) {
+        const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + m * o_stride + h * HD + d));
+        const float2 b = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dout + m * do_stride + h * HD + d));
+        acc += a.x * b.x + a.y * b.y;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) D[(long long)h * M + m] = acc;
+}
+
+// dq (fp32 accumulator, [M, H*HD]) -> inverse RoPE -> bf16 q columns of dqkv. In the same pass the
+// k columns of dqkv (already bf16, written by the backward kernel) get their inverse RoPE in place.
+__global__ void attn_bwd_finish_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv,
+                                       const float* __restrict__ table, long long M, int T, int H, int KV, int HD,
+                                       long long stride, int apply_rope) {
+    const int vph = HD / 8;
+    const long long total = M * (H + KV) * vph;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int v = int(i % vph);
+        const long long t = i / vph;
+        const int h = int(t % (H + KV));
+        const long long m = t / (H + KV);
+        float f[8];
+        __nv_bfloat16* dst = dqkv + m * stride + h * HD + v * 8;
+        if (h < H) {
+            const float4* src = reinterpret_cast<const float4*>(dq_acc + m * (H * HD) + h * HD + v * 8);
+            const float4 a = src[0], b = src[1];
+            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+        } else {
+            const uint4 u = *reinterpret_cast<const uint4*>(dst);
+            float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+            f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = cc.x; f[5] = cc.y; f[6] = d.x; f[7] = d.y;
+        }
+        float o[8];
+        if (apply_rope) {
+            const int pos = int(m % T);
+            const float4* cs = reinterpret_cast<const float4*>(table + ((long long)pos * (HD / 2) + v * 4) * 2);
+            const float4 c0 = cs[0], c1 = cs[1];
+            const float co[4] = {c0.x, c0.z, c1.x, c1.z};
+            const float si[4] = {-c0.y, -c0.w, -c1.y, -c1.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                o[2 * k] = f[2 * k] * co[k] - f[2 * k + 1] * si[k];
+                o[2 * k + 1] = f[2 * k] * si[k] + f[2 * k + 1] * co[k];
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = f[k];
+        }
+        uint4 u;
+        u.x = pack_bf16x2(o[0], o[1]); u.y = pack_bf16x2(o[2], o[3]); u.z = pack_bf16x2(o[4], o[5]); u.w = pack_bf16x2(o[6], o[7]);
+        *reinterpret_cast<uint4*>(dst) = u;
+    }
+}
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
+
+template <int HD>
+static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t st) {
+    using Cfg = AttnBwdCfg<HD>;
+    auto kern = attn_bwd_kernel<HD>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -20;
+        configured = true;
+    }
+    dim3 grid(p.n_tiles, p.KV);
+    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(tq, tdo, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}
+
+}  // namespace pb
+
+// dq_acc: fp32 [M, H*HD] scratch (zeroed here); D: fp32 [H, M] scratch. Writes all of dqkv.
+// rope_table != null: the inverse rotation is applied to dq and dk on the way out.
+extern "C" int pb_attn_bwd(const void* qkv, const void* o, const void* dout, const float* lse2, const int* seq_start,
+                           void* dqkv, float* dq_acc, float* D, const float* rope_table, int T, int M, int H, int KV, int HD,
+                           long long qkv_stride, long long o_stride, long long do_stride, long long dqkv_stride, float scale,
+                           int* status, void* stream) {
+    using namespace pb;
+    if (HD != 64 && HD != 128) return -1;
+    if (H % KV) return -1;
+    if ((qkv_stride % 8) || (o_stride % 8) || (do_stride % 8) || (dqkv_stride % 8)) return -2;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    CUtensorMap tq, tdo;
+    int rc = make_tmap_bf16_2d(&tq, qkv, uint64_t(H + 2 * KV) * HD, M, qkv_stride, 64, 128);
+    if (rc) return rc;
+    rc = make_tmap_bf16_2d(&tdo, dout, uint64_t(H) * HD, M, do_stride, 64, 128);
+    if (rc) return rc;
+    if (cudaMemsetAsync(dq_acc, 0, size_t(M) * H * HD * sizeof(float), st) != cudaSuccess) return -40;
+    {
+        const long long warps = (long long)M * H;
+        attn_bwd_prep_kernel<<<unsigned((warps + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, D, M, H,
+                                                                         HD, o_stride, do_stride);
+    }
+    AttnBwdParams p;
+    p.M = M; p.H = H; p.KV = KV; p.n_tiles = (M + 127) / 128; p.seq_start = seq_start; p.lse2 = lse2; p.D = D;
+    p.dq_acc = dq_acc; p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv); p.dqkv_stride = dqkv_stride;
+    p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    rc = HD == 64 ? launch_attn_bwd<64>(tq, tdo, p, st) : launch_attn_bwd<128>(tq, tdo, p, st);
+    if (rc) return rc;
+    const long long total = (long long)M * (H + KV) * (HD / 8);
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    attn_bwd_finish_kernel<<<unsigned(blocks), 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, rope_table, M, T, H, KV, HD, dqkv_stride,
+                                                              rope_table != nullptr);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}

@@ -34,7 +34,9 @@ struct AttnFwdCfg {
     static constexpr int TILE_BYTES = 128 * HD * 2;          // one Q / K / V tile
     static constexpr int P_BYTES = 128 * 128 * 2;
     static constexpr int KV_STAGES = 2;
-    static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 1024 + 128;
+    // two CTAs of the HD=64 variant must fit one SM, so there is no alignment slack: the kernel
+    // checks that the dynamic shared window is 1024-byte aligned and reports an error otherwise
+    static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 128;
     static constexpr int TMEM_COLS = 256;                    // S: 128 cols, O: HD cols
 };
 
@@ -43,9 +45,13 @@ __global__ void __launch_bounds__(192, (HD == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     using Cfg = AttnFwdCfg<HD>;
     constexpr int NB = HD / 64;   // 64-column swizzle blocks per tile
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    if (base & 1023u) {
+        if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, PB_ERR_TIMEOUT_MISC | 0x80);
+        return;
+    }
+    uint8_t* gen = smem_raw;
     const uint32_t sQ = base;
     const uint32_t sK = sQ + Cfg::TILE_BYTES;                           // [2]
     const uint32_t sV = sK + Cfg::KV_STAGES * Cfg::TILE_BYTES;           // [2]

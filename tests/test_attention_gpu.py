@@ -1,0 +1,66 @@
+"""tcgen05 flash attention (fwd + bwd) against dense fp32 PyTorch attention."""
+import pytest
+import torch
+
+from prime_b200.ops import attention as A
+from prime_b200.ops import kernels as ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def _case(B, T, H, KV, hd, packed, seed=0):
+    torch.manual_seed(seed)
+    M = B * T
+    qkv = (torch.randn(M, (H + 2 * KV) * hd, device="cuda") * 0.7).bfloat16()
+    if packed:
+        g = torch.Generator().manual_seed(seed)
+        seqlens = []
+        for _ in range(B):
+            cuts = sorted(set(torch.randint(1, T, (3,), generator=g).tolist()))
+            lens = [b - a for a, b in zip([0] + cuts, cuts + [T])]
+            seqlens.append(lens)
+        ss = A.seq_start_from_seqlens(seqlens, T, "cuda")
+    else:
+        ss = A.seq_start_from_batch(B, T, "cuda")
+    return qkv, ss
+
+
+@pytest.mark.parametrize("B,T,H,KV,hd", [(2, 256, 4, 4, 64), (1, 512, 4, 2, 64), (2, 384, 4, 1, 128), (1, 1024, 2, 2, 128)])
+@pytest.mark.parametrize("packed", [False, True])
+def test_attention_fwd_bwd(B, T, H, KV, hd, packed):
+    qkv, ss = _case(B, T, H, KV, hd, packed)
+    M = B * T
+    o, lse2 = A.attention_fwd(qkv, ss, H, KV, hd)
+    torch.cuda.synchronize()
+    ops.check_status()
+    x = qkv.float().requires_grad_(True)
+    ref = A.attention_reference(x, ss, H, KV, hd)
+    assert _rel(o, ref) < 2e-2
+    _, lse_ref = A.attention_fwd(qkv.cpu(), ss.cpu(), H, KV, hd)
+    assert (lse2.cpu() - lse_ref).abs().max().item() < 5e-2
+    dout = (torch.randn(M, H * hd, device="cuda") * 0.5).bfloat16()
+    (gref,) = torch.autograd.grad(ref, x, dout.float())
+    dqkv = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd)
+    torch.cuda.synchronize()
+    ops.check_status()
+    q_end, k_end = H * hd, (H + KV) * hd
+    assert _rel(dqkv[:, k_end:], gref[:, k_end:]) < 3e-2, "dV"
+    assert _rel(dqkv[:, q_end:k_end], gref[:, q_end:k_end]) < 3e-2, "dK"
+    assert _rel(dqkv[:, :q_end], gref[:, :q_end]) < 3e-2, "dQ"
+
+
+def test_attention_bwd_with_fused_inverse_rope():
+    B, T, H, KV, hd = 2, 256, 4, 2, 64
+    qkv, ss = _case(B, T, H, KV, hd, False, seed=3)
+    tab = ops.rope_table(T, hd, 10000.0, "cuda")
+    o, lse2 = A.attention_fwd(qkv, ss, H, KV, hd)
+    dout = torch.randn(B * T, H * hd, device="cuda").bfloat16()
+    plain = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd)
+    want = ops.rope_(plain.clone(), tab, T, H + KV, hd, backward=True)
+    got = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd, rope_table=tab, seq_len=T)
+    assert _rel(got, want) < 1.5e-2
+    ops.check_status()
