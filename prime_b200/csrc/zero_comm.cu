@@ -1,0 +1,306 @@
+// ZeRO-3 collectives fused with their consumers, over NVLink peer memory (symmetric buffers).
+//
+// Each rank holds the full bf16/fp32 gradient buffer it just produced in symmetric memory and a
+// table `peers[r]` of every rank's copy of that buffer. The reference does this with FSDP2 +
+// NCCL reduce-scatter / all-gather plus separate foreach kernels (src/zeroband/train.py:150-168,
+// 365-372); here the collective is executed by the kernel that also does the math:
+//
+//   pb_zero_reduce_grads : reduce-scatter by PULL. For every segment this rank owns, load the
+//                          slice from all W ranks with plain P2P ld.global (rotated start peer so
+//                          the W ranks do not hit the same GPU at once), sum in fp32 in fixed rank
+//                          order (bit-identical on every run), scale, write the fp32 shard and
+//                          accumulate the sum of squares needed for global-norm clipping.
+//   pb_zero_adamw_gather : sharded AdamW fused with the all-gather by PUSH. Each updated value is
+//                          converted to bf16 and stored straight into every rank's parameter
+//                          buffer with P2P st.global, so no gathered copy is ever staged.
+//   pb_peer_barrier      : one-CTA epoch barrier on per-peer flags (st.release.sys / ld.acquire.sys)
+//                          with a bounded spin that reports PB_ERR_TIMEOUT_PEER instead of hanging.
+//   pb_allreduce_scalars : all-reduce of a few fp32 scalars through the flag pads, summed in rank
+//                          order so every rank gets the same bits.
+// No TMA multicast and no library collective is involved anywhere in this file.
+#include "common.cuh"
+
+namespace pb {
+
+constexpr int MAX_SEGS = 16;
+constexpr int MAX_RANKS = 16;
+
+struct SegTable {
+    int n;
+    long long full_off[MAX_SEGS];
+    long long shard_off[MAX_SEGS];
+    long long numel[MAX_SEGS];
+};
+struct PeerTable {
+    int world, rank;
+    void* ptr[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// pads[r] points at rank r's flag pad: int[slots][MAX_RANKS]. Thread t signals peer t and waits
+// for peer t's signal in its own pad. Epochs only grow, so no reset race exists.
+__global__ void peer_barrier_kernel(PeerTable pads, int slot, int epoch, int* status) {
+    const int t = threadIdx.x;
+    if (t >= pads.world) return;
+    __threadfence_system();
+    int* remote = reinterpret_cast<int*>(pads.ptr[t]) + slot * MAX_RANKS + pads.rank;
+    st_release_sys(remote, epoch);
+    const int* mine = reinterpret_cast<const int*>(pads.ptr[pads.rank]) + slot * MAX_RANKS + t;
+    const uint64_t t0 = globaltimer_ns();
+    while (ld_acquire_sys(mine) < epoch) {
+        if (globaltimer_ns() - t0 > PB_WAIT_BUDGET_NS) {
+            if (status) atomicCAS(status, 0, PB_ERR_TIMEOUT_PEER | (t << 8));
+            return;
+        }
+        __nanosleep(200);
+    }
+}
+
+// vals[pads.rank][slot][0..n) of every rank -> summed into out[0..n), identical order everywhere.
+// data pads: float[slots][2 (epoch parity)][MAX_RANKS][8]; the parity double-buffer lets a fast rank start
+// the next reduction while a slow one still sums the previous values
+__global__ void allreduce_scalars_kernel(PeerTable flag_pads, PeerTable data_pads, int slot, int epoch,
+                                         const float* __restrict__ in, float* __restrict__ out, int n, int* status) {
+    const int t = threadIdx.x;
+    if (t < flag_pads.world) {
+        float* remote = reinterpret_cast<float*>(data_pads.ptr[t]) + ((slot * 2 + (epoch & 1)) * MAX_RANKS + flag_pads.rank) * 8;
+        for (int i = 0; i < n; ++i) remote[i] = in[i];
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(flag_pads.ptr[t]) + slot * MAX_RANKS + flag_pads.rank, epoch);
+        const int* mine = reinterpret_cast<const int*>(flag_pads.ptr[flag_pads.rank]) + slot * MAX_RANKS + t;
+        const uint64_t t0 = globaltimer_ns();
+        bool ok = true;
+        while (ld_acquire_sys(mine) < epoch) {
+            if (globaltimer_ns() - t0 > PB_WAIT_BUDGET_NS) {
+                if (status) atomicCAS(status, 0, PB_ERR_TIMEOUT_PEER | (t << 8));
+                ok = false;
+                break;
+            }
+            __nanosleep(200);
+        }
+        (void)ok;
+    }
+    __syncthreads();
+    if (t < n) {
+        const volatile float* mine = reinterpret_cast<const volatile float*>(data_pads.ptr[flag_pads.rank]) + (slot * 2 + (epoch & 1)) * MAX_RANKS * 8;
+        float s = 0.f;
+        for (int r = 0; r < flag_pads.world; ++r) s += mine[r * 8 + t];
+        out[t] = s;
+    }
+}
+
+template <typename G>
+__device__ __forceinline__ float ld_grad(const G* p) { return float(*p); }
+
+// Reduce-scatter by pull + cast/scale + sum of squares. grid-stride over the segment elements.
+template <typename G>
+__global__ void __launch_bounds__(256) zero_reduce_grads_kernel(PeerTable peers, SegTable segs, float* __restrict__ grad_shard,
+                                                                float scale, float* __restrict__ sumsq_partial) {
+    __shared__ float red[8];
+    float ss = 0.f;
+    const int W = peers.world;
+    for (int s = 0; s < segs.n; ++s) {
+        const long long n = segs.numel[s];
+        const long long fo = segs.full_off[s];
+        float* dst = grad_shard + segs.shard_off[s];
+        // vector path: 8 elements per thread per step when everything is 16-byte aligned
+        const bool vec_ok = (fo % 8 == 0) && (segs.shard_off[s] % 4 == 0) && sizeof(G) == 2;
+        const long long nvec = vec_ok ? n / 8 : 0;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            // issue all peer loads first (W independent 16-byte loads in flight), then add in rank order
+            uint4 v[MAX_RANKS];
+#pragma unroll
+            for (int r = 0; r < MAX_RANKS; ++r)
+                if (r < W) v[r] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peers.ptr[r]) + fo) + i);
+#pragma unroll
+            for (int r = 0; r < MAX_RANKS; ++r)
+                if (r < W) {
+                    const float2 a = unpack_bf16x2(v[r].x), b = unpack_bf16x2(v[r].y), c = unpack_bf16x2(v[r].z), d = unpack_bf16x2(v[r].w);
+                    acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+                }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { acc[k] *= scale; ss += acc[k] * acc[k]; }
+            reinterpret_cast<float4*>(dst)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        }
+        for (long long i = nvec * 8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+            float acc = 0.f;
+            for (int r = 0; r < W; ++r) acc += ld_grad(reinterpret_cast<const G*>(peers.ptr[r]) + fo + i);
+            acc *= scale;
+            ss += acc * acc;
+            dst[i] = acc;
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < (blockDim.x >> 5); ++i) t += red[i];
+        sumsq_partial[blockIdx.x] = t;
+    }
+}
+
+// fixed-order sum of `n` partials -> out[0] (+)=
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, int n, float* __restrict__ out, int accumulate) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < n; ++i) t += partial[i];
+        out[0] = accumulate ? out[0] + t : t;
+    }
+}
+
+// Sharded AdamW + push all-gather. gnorm_sq: device scalar with the GLOBAL sum of squared grads.
+__global__ void __launch_bounds__(256) zero_adamw_gather_kernel(PeerTable params, SegTable segs, float* __restrict__ master,
+                                                                const float* __restrict__ grad_shard, float* __restrict__ m,
+                                                                float* __restrict__ v, float lr, float beta1, float beta2, float eps,
+                                                                float wd, float bc1, float bc2, const float* __restrict__ gnorm_sq,
+                                                                float max_norm) {
+    float clip = 1.f;
+    if (gnorm_sq && max_norm > 0.f) {
+        const float c = max_norm / (sqrtf(*gnorm_sq) + 1e-6f);
+        clip = c < 1.f ? c : 1.f;
+    }
+    const int W = params.world;
+    for (int s = 0; s < segs.n; ++s) {
+        const long long n = segs.numel[s], fo = segs.full_off[s], so = segs.shard_off[s];
+        const bool vec_ok = (fo % 8 == 0) && (so % 4 == 0);
+        const long long nvec = vec_ok ? n / 8 : 0;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+            float p[8], g[8], mm[8], vv[8];
+            *reinterpret_cast<float4*>(p) = reinterpret_cast<const float4*>(master + so)[2 * i];
+            *reinterpret_cast<float4*>(p + 4) = reinterpret_cast<const float4*>(master + so)[2 * i + 1];
+            *reinterpret_cast<float4*>(g) = reinterpret_cast<const float4*>(grad_shard + so)[2 * i];
+            *reinterpret_cast<float4*>(g + 4) = reinterpret_cast<const float4*>(grad_shard + so)[2 * i + 1];
+            *reinterpret_cast<float4*>(mm) = reinterpret_cast<const float4*>(m + so)[2 * i];
+            *reinterpret_cast<float4*>(mm + 4) = reinterpret_cast<const float4*>(m + so)[2 * i + 1];
+            *reinterpret_cast<float4*>(vv) = reinterpret_cast<const float4*>(v + so)[2 * i];
+            *reinterpret_cast<float4*>(vv + 4) = reinterpret_cast<const float4*>(v + so)[2 * i + 1];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float gi = g[k] * clip;
+                p[k] *= (1.f - lr * wd);
+                mm[k] = beta1 * mm[k] + (1.f - beta1) * gi;
+                vv[k] = beta2 * vv[k] + (1.f - beta2) * gi * gi;
+                p[k] -= (lr / bc1) * (mm[k] / (sqrtf(vv[k]) / bc2 + eps));
+            }
+            reinterpret_cast<float4*>(master + so)[2 * i] = *reinterpret_cast<float4*>(p);
+            reinterpret_cast<float4*>(master + so)[2 * i + 1] = *reinterpret_cast<float4*>(p + 4);
+            reinterpret_cast<float4*>(m + so)[2 * i] = *reinterpret_cast<float4*>(mm);
+            reinterpret_cast<float4*>(m + so)[2 * i + 1] = *reinterpret_cast<float4*>(mm + 4);
+            reinterpret_cast<float4*>(v + so)[2 * i] = *reinterpret_cast<float4*>(vv);
+            reinterpret_cast<float4*>(v + so)[2 * i + 1] = *reinterpret_cast<float4*>(vv + 4);
+            uint4 o;
+            o.x = pack_bf16x2(p[0], p[1]); o.y = pack_bf16x2(p[2], p[3]); o.z = pack_bf16x2(p[4], p[5]); o.w = pack_bf16x2(p[6], p[7]);
+#pragma unroll
+            for (int r = 0; r < MAX_RANKS; ++r)
+                if (r < W) {
+                    const int dstr = (params.rank + r) % W;   // rotate so ranks push to different GPUs at once
+                    reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.ptr[dstr]) + fo)[i] = o;
+                }
+        }
+        for (long long i = nvec * 8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+            const float gi = grad_shard[so + i] * clip;
+            float pi = master[so + i] * (1.f - lr * wd);
+            const float mi = beta1 * m[so + i] + (1.f - beta1) * gi;
+            const float vi = beta2 * v[so + i] + (1.f - beta2) * gi * gi;
+            pi -= (lr / bc1) * (mi / (sqrtf(vi) / bc2 + eps));
+            master[so + i] = pi; m[so + i] = mi; v[so + i] = vi;
+            const __nv_bfloat16 o = __float2bfloat16(pi);
+            for (int r = 0; r < W; ++r) reinterpret_cast<__nv_bfloat16*>(params.ptr[(params.rank + r) % W])[fo + i] = o;
+        }
+    }
+}
+
+// master fp32 shard -> bf16 pushed into every rank's parameter buffer (initial broadcast / after a
+// checkpoint load or a DiLoCo outer step rewrote the master shard)
+__global__ void __launch_bounds__(256) zero_push_params_kernel(PeerTable params, SegTable segs, const float* __restrict__ master) {
+    const int W = params.world;
+    for (int s = 0; s < segs.n; ++s) {
+        const long long n = segs.numel[s], fo = segs.full_off[s], so = segs.shard_off[s];
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+            const __nv_bfloat16 o = __float2bfloat16(master[so + i]);
+            for (int r = 0; r < W; ++r) reinterpret_cast<__nv_bfloat16*>(params.ptr[(params.rank + r) % W])[fo + i] = o;
+        }
+    }
+}
+
+static PeerTable make_peers(void* const* ptrs, int world, int rank) {
+    PeerTable t{};
+    t.world = world; t.rank = rank;
+    for (int r = 0; r < world && r < MAX_RANKS; ++r) t.ptr[r] = ptrs[r];
+    return t;
+}
+static SegTable make_segs(int n, const long long* full_off, const long long* shard_off, const long long* numel) {
+    SegTable s{};
+    s.n = n;
+    for (int i = 0; i < n; ++i) { s.full_off[i] = full_off[i]; s.shard_off[i] = shard_off[i]; s.numel[i] = numel[i]; }
+    return s;
+}
+
+}  // namespace pb
+
+using namespace pb;
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int pb_zero_max_segs() { return MAX_SEGS; }
+extern "C" int pb_zero_max_ranks() { return MAX_RANKS; }
+
+extern "C" int pb_peer_barrier(void* const* pad_ptrs, int world, int rank, int slot, int epoch, int* status, void* stream) {
+    if (world > MAX_RANKS) return -1;
+    peer_barrier_kernel<<<1, 32, 0, ST(stream)>>>(make_peers(pad_ptrs, world, rank), slot, epoch, status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}
+
+extern "C" int pb_allreduce_scalars(void* const* flag_pads, void* const* data_pads, int world, int rank, int slot, int epoch,
+                                    const float* in, float* out, int n, int* status, void* stream) {
+    if (world > MAX_RANKS || n > 8) return -1;
+    allreduce_scalars_kernel<<<1, 32, 0, ST(stream)>>>(make_peers(flag_pads, world, rank), make_peers(data_pads, world, rank), slot,
+                                                       epoch, in, out, n, status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}
+
+// sumsq_out (+)= sum of squares of the reduced, scaled shard values of these segments.
+// partial: scratch of >= ctas floats.
+extern "C" int pb_zero_reduce_grads(void* const* peer_grads, int world, int rank, int grad_fp32, int nseg,
+                                    const long long* full_off, const long long* shard_off, const long long* numel,
+                                    float* grad_shard, float scale, float* partial, float* sumsq_out, int accumulate, int ctas,
+                                    void* stream) {
+    if (world > MAX_RANKS || nseg > MAX_SEGS) return -1;
+    PeerTable pt = make_peers(peer_grads, world, rank);
+    SegTable sg = make_segs(nseg, full_off, shard_off, numel);
+    if (grad_fp32) zero_reduce_grads_kernel<float><<<ctas, 256, 0, ST(stream)>>>(pt, sg, grad_shard, scale, partial);
+    else zero_reduce_grads_kernel<__nv_bfloat16><<<ctas, 256, 0, ST(stream)>>>(pt, sg, grad_shard, scale, partial);
+    reduce_partials_kernel<<<1, 32, 0, ST(stream)>>>(partial, ctas, sumsq_out, accumulate);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}
+
+extern "C" int pb_zero_adamw_gather(void* const* peer_params, int world, int rank, int nseg, const long long* full_off,
+                                    const long long* shard_off, const long long* numel, float* master, const float* grad_shard,
+                                    float* m, float* v, float lr, float beta1, float beta2, float eps, float wd, int step,
+                                    const float* gnorm_sq, float max_norm, int ctas, void* stream) {
+    if (world > MAX_RANKS || nseg > MAX_SEGS) return -1;
+    const float bc1 = 1.f - powf(beta1, float(step));
+    const float bc2 = sqrtf(1.f - powf(beta2, float(step)));
+    zero_adamw_gather_kernel<<<ctas, 256, 0, ST(stream)>>>(make_peers(peer_params, world, rank),
+                                                           make_segs(nseg, full_off, shard_off, numel), master, grad_shard, m, v, lr,
+                                                           beta1, beta2, eps, wd, bc1, bc2, gnorm_sq, max_norm);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}
+
+extern "C" int pb_zero_push_params(void* const* peer_params, int world, int rank, int nseg, const long long* full_off,
+                                   const long long* shard_off, const long long* numel, const float* master, int ctas, void* stream) {
+    if (world > MAX_RANKS || nseg > MAX_SEGS) return -1;
+    zero_push_params_kernel<<<ctas, 256, 0, ST(stream)>>>(make_peers(peer_params, world, rank),
+                                                          make_segs(nseg, full_off, shard_off, numel), master);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}

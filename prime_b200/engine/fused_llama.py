@@ -1,0 +1,447 @@
+"""Fused Llama training engine for B200: the network as an explicit kernel schedule.
+
+Instead of tracing modules through autograd and a compiler (the reference wraps its
+``Transformer`` in FSDP2 + ``torch.compile``, src/zeroband/train.py:150-168, 208-211), the
+engine owns flat parameter / gradient / optimizer buffers (see :mod:`.layout`) and runs forward,
+backward and the optimizer as a fixed sequence of hand-written sm_100a kernels on one CUDA
+stream, with the ZeRO-3 collectives on a second stream:
+
+  forward   embedding -> L x [rmsnorm, fused QKV GEMM, RoPE, flash attention, wo GEMM (+residual
+            epilogue), rmsnorm, fused w1|w3 GEMM, SwiGLU, w2 GEMM (+residual epilogue)]
+  head      final rmsnorm, then per token chunk: logits GEMM, cross-entropy with in-place
+            gradient, dgrad + wgrad GEMMs (logits never exist for more than one chunk)
+  backward  per block: 4 dgrad + 4 wgrad GEMMs, SwiGLU bwd, flash attention bwd with the inverse
+            RoPE folded into its last pass, 2 rmsnorm bwd (residual gradient folded in)
+  update    per parameter group: reduce-scatter-by-pull + cast/scale + sum-of-squares, then one
+            scalar all-reduce for the global norm, then sharded AdamW that pushes the new bf16
+            values into every rank's replica (all-gather by push)
+
+The bf16 parameter replica stays resident on every GPU (180 GB HBM makes ZeRO-3's re-gather
+before every use unnecessary); what is sharded is everything fp32: master weights, AdamW moments
+and the reduced gradient.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .. import native
+from ..models.llama import ModelArgs
+from ..native import check, ptr, stream_ptr
+from ..ops import attention as A
+from ..ops import kernels as K
+from .layout import ParamLayout, llama_layout
+
+native.register_cuda_sigs({
+    "pb_zero_max_segs": [],
+    "pb_zero_max_ranks": [],
+    "pb_peer_barrier": [native.vp, native.i32, native.i32, native.i32, native.i32, native.vp, native.vp],
+    "pb_allreduce_scalars": [native.vp, native.vp, native.i32, native.i32, native.i32, native.i32, native.vp, native.vp,
+                             native.i32, native.vp, native.vp],
+    "pb_zero_reduce_grads": [native.vp, native.i32, native.i32, native.i32, native.i32, native.vp, native.vp, native.vp,
+                             native.vp, native.f32, native.vp, native.vp, native.i32, native.i32, native.vp],
+    "pb_zero_adamw_gather": [native.vp, native.i32, native.i32, native.i32, native.vp, native.vp, native.vp, native.vp,
+                             native.vp, native.vp, native.vp, native.f32, native.f32, native.f32, native.f32, native.f32,
+                             native.i32, native.vp, native.f32, native.i32, native.vp],
+    "pb_zero_push_params": [native.vp, native.i32, native.i32, native.i32, native.vp, native.vp, native.vp, native.vp,
+                            native.i32, native.vp],
+})
+
+
+class _SegArrays:
+    """ctypes arrays describing the segments of one group for one rank."""
+
+    def __init__(self, segs):
+        segs = [s for s in segs if s.numel > 0]
+        self.n = len(segs)
+        arr = C.c_longlong * max(self.n, 1)
+        self.full = arr(*[s.full_offset for s in segs])
+        self.shard = arr(*[s.shard_offset for s in segs])
+        self.numel = arr(*[s.numel for s in segs])
+        self.total = sum(s.numel for s in segs)
+
+
+class LocalComm:
+    """Single-rank stand-in for the symmetric-memory communicator: buffers are ordinary tensors."""
+    world = 1
+    rank = 0
+
+    def alloc(self, numel: int, dtype: torch.dtype, device) -> torch.Tensor:
+        return torch.zeros(numel, dtype=dtype, device=device)
+
+    def peer_ptrs(self, t: torch.Tensor):
+        return (C.c_void_p * 1)(t.data_ptr())
+
+    def barrier(self, stream=None):
+        pass
+
+    def allreduce_scalars(self, src: torch.Tensor, dst: torch.Tensor, n: int):
+        dst[:n].copy_(src[:n])
+
+
+class FusedLlama:
+    """See module docstring. One instance per process / GPU."""
+
+    def __init__(self, args: ModelArgs, device: torch.device | str = "cuda", comm=None, grad_dtype=torch.bfloat16,
+                 ac_ckpt: bool | int = False, ce_chunk_tokens: int = 8192, z_mode: int = K.Z_NONE, z_weight: float = 0.0,
+                 comm_ctas: int = 32):
+        self.args = args
+        self.device = torch.device(device)
+        self.comm = comm if comm is not None else LocalComm()
+        self.world, self.rank = self.comm.world, self.comm.rank
+        self.layout: ParamLayout = llama_layout(args, self.world)
+        self.grad_dtype = grad_dtype
+        self.ac_every = (1 if ac_ckpt is True else int(ac_ckpt)) if ac_ckpt else 0
+        self.ce_chunk = ce_chunk_tokens
+        self.z_mode, self.z_weight = z_mode, z_weight
+        self.comm_ctas = comm_ctas
+        lay = self.layout
+        dev = self.device
+        # flat buffers --------------------------------------------------------------------------
+        self.params = self.comm.alloc(lay.full_numel, torch.bfloat16, dev)       # replica, symmetric
+        self.grads = self.comm.alloc(lay.full_numel, grad_dtype, dev)             # local grads, symmetric
+        n_shard = lay.shard_numel[self.rank]
+        self.master = torch.zeros(n_shard, dtype=torch.float32, device=dev)
+        self.exp_avg = torch.zeros(n_shard, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(n_shard, dtype=torch.float32, device=dev)
+        self.grad_shard = torch.zeros(n_shard, dtype=torch.float32, device=dev)
+        self._peer_params = self.comm.peer_ptrs(self.params)
+        self._peer_grads = self.comm.peer_ptrs(self.grads)
+        self._segs = [_SegArrays(lay.group_segments(self.rank, g)) for g in range(len(lay.groups))]
+        max_segs = native.cuda().pb_zero_max_segs() if dev.type == "cuda" else 16
+        assert all(s.n <= max_segs for s in self._segs)
+        self._partials = torch.zeros(4096, dtype=torch.float32, device=dev)
+        self._norm_local = torch.zeros(8, dtype=torch.float32, device=dev)
+        self._norm_global = torch.zeros(8, dtype=torch.float32, device=dev)
+        self.opt_step = 0
+        self._accum = False            # gradients hold a partial sum from earlier micro-batches
+        self._ws: dict[str, torch.Tensor] = {}
+        self._rope = K.rope_table(args.max_seq_len * 2, args.head_dim, args.rope_theta, dev)
+        self._seq_start_cache: dict[tuple[int, int], torch.Tensor] = {}
+        self.comm_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+        # parameter views -----------------------------------------------------------------------
+        self.w: dict[str, torch.Tensor] = {}
+        self.g: dict[str, torch.Tensor] = {}
+        for p in lay.params:
+            self.w[p.name] = self.params[p.offset: p.offset + p.numel].view(p.shape)
+            self.g[p.name] = self.grads[p.offset: p.offset + p.numel].view(p.shape)
+        D, F, hd, H, KV = args.dim, args.hidden_dim, args.head_dim, args.n_heads, args.kv_heads
+        self.wqkv, self.gqkv, self.w13, self.g13 = [], [], [], []
+        for i in range(args.n_layers):
+            q = lay.params[lay.by_name[f"layers.{i}.attention.wq.weight"]]
+            n = (H + 2 * KV) * hd * D
+            self.wqkv.append(self.params[q.offset: q.offset + n].view((H + 2 * KV) * hd, D))
+            self.gqkv.append(self.grads[q.offset: q.offset + n].view((H + 2 * KV) * hd, D))
+            w1 = lay.params[lay.by_name[f"layers.{i}.feed_forward.w1.weight"]]
+            self.w13.append(self.params[w1.offset: w1.offset + 2 * F * D].view(2 * F, D))
+            self.g13.append(self.grads[w1.offset: w1.offset + 2 * F * D].view(2 * F, D))
+
+    # ------------------------------------------------------------------------------------------
+    # parameter I/O
+    # ------------------------------------------------------------------------------------------
+    def shard_view(self, buf: torch.Tensor, name: str) -> torch.Tensor:
+        """This rank's dim-0 slice of parameter ``name`` inside a shard-layout buffer."""
+        lay = self.layout
+        i = lay.by_name[name]
+        s = lay.segments[self.rank][i]
+        p = lay.params[i]
+        return buf[s.shard_offset: s.shard_offset + s.numel].view((s.row_end - s.row_start,) + p.shape[1:])
+
+    def named_master_shards(self):
+        for p in self.layout.params:
+            yield p.name, self.shard_view(self.master, p.name)
+
+    @torch.no_grad()
+    def load_from_module(self, model: torch.nn.Module) -> None:
+        """Copy fp32 weights of an eager ``Transformer`` into the master shard, then publish bf16."""
+        sd = dict(model.named_parameters())
+        for p in self.layout.params:
+            s = self.layout.segments[self.rank][self.layout.by_name[p.name]]
+            src = sd[p.name].detach()[s.row_start: s.row_end]
+            self.shard_view(self.master, p.name).copy_(src.to(self.device, torch.float32))
+        self.publish_params()
+
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0, std: float | None = None) -> None:
+        """Plain N(0, std) initialisation (norm weights = 1) generated shard-by-shard on device;
+        every rank draws only the rows it owns from a per-parameter seeded generator."""
+        std = self.args.init_std if std is None else std
+        for idx, p in enumerate(self.layout.params):
+            view = self.shard_view(self.master, p.name)
+            if "norm" in p.name:
+                view.fill_(1.0)
+                continue
+            g = torch.Generator(device=self.device)
+            g.manual_seed(seed * 100003 + idx * 131 + self.rank)
+            view.normal_(0.0, std, generator=g)
+        self.publish_params()
+
+    def publish_params(self) -> None:
+        """master fp32 shard -> bf16 into every rank's replica (all-gather by push)."""
+        if self.device.type != "cuda":
+            for name, v in self.named_master_shards():
+                i = self.layout.by_name[name]
+                s = self.layout.segments[self.rank][i]
+                self.params[s.full_offset: s.full_offset + s.numel].copy_(v.reshape(-1).to(torch.bfloat16))
+            return
+        lib = native.cuda()
+        self.comm.barrier()
+        for g, sa in enumerate(self._segs):
+            if sa.n:
+                check(lib.pb_zero_push_params(self._peer_params, self.world, self.rank, sa.n, sa.full, sa.shard, sa.numel,
+                                              ptr(self.master), self.comm_ctas, stream_ptr()), "pb_zero_push_params")
+        self.comm.barrier()
+
+    # ------------------------------------------------------------------------------------------
+    # workspace
+    # ------------------------------------------------------------------------------------------
+    def _buf(self, name: str, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        t = self._ws.get(name)
+        n = math.prod(shape)
+        if t is None or t.numel() < n or t.dtype != dtype:
+            t = torch.empty(n, dtype=dtype, device=self.device)
+            self._ws[name] = t
+        return t[:n].view(shape)
+
+    def _saved(self, layer: int, name: str, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        # with activation checkpointing only the block input is kept per layer
+        key = f"L{layer}.{name}" if (not self._is_ckpt(layer) or name == "x") else f"Lshared.{name}"
+        return self._buf(key, shape, dtype)
+
+    def _is_ckpt(self, layer: int) -> bool:
+        return self.ac_every > 0 and layer % self.ac_every == 0
+
+    def default_seq_start(self, B: int, T: int) -> torch.Tensor:
+        k = (B, T)
+        if k not in self._seq_start_cache:
+            self._seq_start_cache[k] = A.seq_start_from_batch(B, T, self.device)
+        return self._seq_start_cache[k]
+
+    # ------------------------------------------------------------------------------------------
+    # forward / backward of one block
+    # ------------------------------------------------------------------------------------------
+    def _block_fwd(self, i: int, x: torch.Tensor, T: int, seq_start: torch.Tensor, out: torch.Tensor) -> None:
+        a = self.args
+        M = x.shape[0]
+        D, F, hd, H, KV = a.dim, a.hidden_dim, a.head_dim, a.n_heads, a.kv_heads
+        pre = f"layers.{i}."
+        xn = self._saved(i, "xn", (M, D))
+        rstd1 = self._saved(i, "rstd1", (M,), torch.float32)
+        K.rmsnorm_fwd(x, self.w[pre + "attention_norm.weight"], a.norm_eps, out=xn, rstd=rstd1)
+        qkv = self._saved(i, "qkv", (M, (H + 2 * KV) * hd))
+        K.gemm(xn, self.wqkv[i], out=qkv)
+        K.rope_(qkv, self._rope, T, H + KV, hd)
+        o = self._saved(i, "o", (M, H * hd))
+        _, lse2 = A.attention_fwd(qkv, seq_start, H, KV, hd, out=o)
+        self._ws[f"L{i}.lse2" if not self._is_ckpt(i) else "Lshared.lse2"] = lse2
+        h = self._saved(i, "h", (M, D))
+        K.gemm(o, self.w[pre + "attention.wo.weight"], out=h, residual=x)
+        hn = self._saved(i, "hn", (M, D))
+        rstd2 = self._saved(i, "rstd2", (M,), torch.float32)
+        K.rmsnorm_fwd(h, self.w[pre + "ffn_norm.weight"], a.norm_eps, out=hn, rstd=rstd2)
+        h13 = self._saved(i, "h13", (M, 2 * F))
+        K.gemm(hn, self.w13[i], out=h13)
+        act = self._saved(i, "act", (M, F))
+        K.swiglu_fwd(h13, out=act)
+        K.gemm(act, self.w[pre + "feed_forward.w2.weight"], out=out, residual=h)
+
+    def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, g: torch.Tensor) -> None:
+        """g[N,K] (+)= dy[M,N]^T x[M,K]"""
+        K.gemm(dy, x, out=g, residual=g if self._accum else None, a_mn=True, b_mn=True)
+
+    def _block_bwd(self, i: int, x: torch.Tensor, dout: torch.Tensor, T: int, seq_start: torch.Tensor, dx: torch.Tensor) -> None:
+        a = self.args
+        M = x.shape[0]
+        D, F, hd, H, KV = a.dim, a.hidden_dim, a.head_dim, a.n_heads, a.kv_heads
+        pre = f"layers.{i}."
+        if self._is_ckpt(i):   # recompute the block's activations into the shared workspace
+            self._block_fwd(i, x, T, seq_start, self._buf("ckpt_out", (M, D)))
+        sv = lambda n, shp, dt=torch.bfloat16: self._saved(i, n, shp, dt)  # noqa: E731
+        xn, rstd1, qkv, o = sv("xn", (M, D)), sv("rstd1", (M,), torch.float32), sv("qkv", (M, (H + 2 * KV) * hd)), sv("o", (M, H * hd))
+        lse2 = self._ws[f"L{i}.lse2" if not self._is_ckpt(i) else "Lshared.lse2"]
+        h, hn, rstd2 = sv("h", (M, D)), sv("hn", (M, D)), sv("rstd2", (M,), torch.float32)
+        h13, act = sv("h13", (M, 2 * F)), sv("act", (M, F))
+        # out = h + act @ w2^T
+        dact = self._buf("dact", (M, F))
+        K.gemm(dout, self.w[pre + "feed_forward.w2.weight"], out=dact, b_mn=True)
+        self._wgrad(dout, act, self.g[pre + "feed_forward.w2.weight"])
+        K.swiglu_bwd(h13, dact, dh13=h13)                       # in place: h13 becomes d(h13)
+        dhn = self._buf("dhn", (M, D))
+        K.gemm(h13, self.w13[i], out=dhn, b_mn=True)
+        self._wgrad(h13, hn, self.g13[i])
+        dh = self._buf("dh", (M, D))
+        K.rmsnorm_bwd(h, self.w[pre + "ffn_norm.weight"], rstd2, dhn, self.g[pre + "ffn_norm.weight"], dres=dout, dx=dh,
+                      accumulate_dw=self._accum)
+        # h = x + o @ wo^T
+        do = self._buf("do", (M, H * hd))
+        K.gemm(dh, self.w[pre + "attention.wo.weight"], out=do, b_mn=True)
+        self._wgrad(dh, o, self.g[pre + "attention.wo.weight"])
+        dqkv = self._buf("dqkv", (M, (H + 2 * KV) * hd))
+        A.attention_bwd(qkv, o, do, lse2, seq_start, H, KV, hd, dqkv=dqkv, rope_table=self._rope, seq_len=T)
+        dxn = self._buf("dxn", (M, D))
+        K.gemm(dqkv, self.wqkv[i], out=dxn, b_mn=True)
+        self._wgrad(dqkv, xn, self.gqkv[i])
+        K.rmsnorm_bwd(x, self.w[pre + "attention_norm.weight"], rstd1, dxn, self.g[pre + "attention_norm.weight"], dres=dh,
+                      dx=dx, accumulate_dw=self._accum)
+
+    # ------------------------------------------------------------------------------------------
+    # full micro-step
+    # ------------------------------------------------------------------------------------------
+    def forward_backward(self, tokens: torch.Tensor, labels: torch.Tensor, seq_start: torch.Tensor | None = None,
+                         loss_scale: float = 1.0, last_microbatch: bool = True) -> dict[str, torch.Tensor]:
+        """One micro-batch: forward, loss, backward; gradients accumulate until ``optimizer_step``.
+        Returns device scalars ``loss`` (mean CE over non-ignored tokens) and ``z_loss``."""
+        a = self.args
+        B, T = tokens.shape
+        M = B * T
+        D, V, L = a.dim, a.vocab_size, a.n_layers
+        if seq_start is None:
+            seq_start = self.default_seq_start(B, T)
+        tok = tokens.reshape(-1)
+        lab = labels.reshape(-1)
+        xs = [self._buf(f"L{i}.x", (M, D)) for i in range(L + 1)]
+        K.embedding_fwd(tok, self.w["tok_embeddings.weight"], out=xs[0])
+        for i in range(L):
+            self._block_fwd(i, xs[i], T, seq_start, xs[i + 1])
+        # ---- head: final norm + chunked linear / cross-entropy / gradient ----
+        hn = self._buf("head.hn", (M, D))
+        rstd = self._buf("head.rstd", (M,), torch.float32)
+        K.rmsnorm_fwd(xs[L], self.w["norm.weight"], a.norm_eps, out=hn, rstd=rstd)
+        dhn = self._buf("head.dhn", (M, D))
+        loss_rows = self._buf("head.loss_rows", (M,), torch.float32)
+        z_rows = self._buf("head.z_rows", (M,), torch.float32)
+        inv = K.count_valid(lab)
+        Vp = (V + 7) // 8 * 8
+        Mc = min(self.ce_chunk, M)
+        logits_buf = self._buf("head.logits", (Mc, Vp))
+        Wout, gWout = self.w["output.weight"], self.g["output.weight"]
+        accum_head = self._accum
+        for c0 in range(0, M, Mc):
+            c1 = min(M, c0 + Mc)
+            lg = logits_buf[: c1 - c0, :V]
+            K.gemm(hn[c0:c1], Wout, out=lg)
+            K.cross_entropy_(lg, lab[c0:c1], inv, loss_rows[c0:c1], z_rows[c0:c1], grad_scale=loss_scale,
+                             z_mode=self.z_mode, z_weight=self.z_weight)
+            K.gemm(lg, Wout, out=dhn[c0:c1], b_mn=True)
+            K.gemm(lg, hn[c0:c1], out=gWout, residual=gWout if accum_head else None, a_mn=True, b_mn=True)
+            accum_head = True
+        out = self._buf("head.scalars", (2,), torch.float32)
+        K.sum_f32(loss_rows, out[0:1], scale_ptr=inv[0:1])
+        K.sum_f32(z_rows, out[1:2], scale_ptr=inv[0:1], scale=self.z_weight)
+        dx = self._buf("dx_a", (M, D))
+        K.rmsnorm_bwd(xs[L], self.w["norm.weight"], rstd, dhn, self.g["norm.weight"], dx=dx, accumulate_dw=self._accum)
+        # ---- blocks in reverse ----
+        other = self._buf("dx_b", (M, D))
+        for i in reversed(range(L)):
+            self._block_bwd(i, xs[i], dx, T, seq_start, other)
+            dx, other = other, dx
+        # ---- embedding ----
+        gE = self.g["tok_embeddings.weight"]
+        if not self._accum:
+            gE.zero_()
+        K.embedding_bwd(tok, dx, gE)
+        self._accum = True
+        return {"loss": out[0], "z_loss": out[1]}
+
+    # ------------------------------------------------------------------------------------------
+    # optimizer
+    # ------------------------------------------------------------------------------------------
+    def optimizer_step(self, lr: float, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1,
+                       max_norm: float = 1.0) -> torch.Tensor:
+        """Reduce-scatter + global-norm clip + sharded AdamW + all-gather. Returns the (device
+        scalar) total gradient norm before clipping."""
+        assert self._accum, "optimizer_step without gradients"
+        self.opt_step += 1
+        if self.device.type != "cuda":
+            return self._optimizer_step_cpu(lr, betas, eps, weight_decay, max_norm)
+        lib = native.cuda()
+        W = self.world
+        self.comm.barrier()                                   # every rank finished writing its grads
+        for g, sa in enumerate(self._segs):
+            if sa.n == 0:
+                continue
+            check(lib.pb_zero_reduce_grads(self._peer_grads, W, self.rank, int(self.grad_dtype == torch.float32), sa.n, sa.full,
+                                           sa.shard, sa.numel, ptr(self.grad_shard), 1.0 / W, ptr(self._partials),
+                                           ptr(self._norm_local), int(g > 0), min(self.comm_ctas * 4, 1024), stream_ptr()),
+                  "pb_zero_reduce_grads")
+        self.comm.allreduce_scalars(self._norm_local, self._norm_global, 1)   # also orders: all ranks done reading grads
+        for g, sa in enumerate(self._segs):
+            if sa.n == 0:
+                continue
+            check(lib.pb_zero_adamw_gather(self._peer_params, W, self.rank, sa.n, sa.full, sa.shard, sa.numel, ptr(self.master),
+                                           ptr(self.grad_shard), ptr(self.exp_avg), ptr(self.exp_avg_sq), lr, betas[0], betas[1],
+                                           eps, weight_decay, self.opt_step, ptr(self._norm_global), max_norm,
+                                           min(self.comm_ctas * 4, 1024), stream_ptr()), "pb_zero_adamw_gather")
+        self.comm.barrier()                                   # every rank's replica is complete
+        self._accum = False
+        return self._norm_global[0].sqrt()
+
+    def _optimizer_step_cpu(self, lr, betas, eps, weight_decay, max_norm) -> torch.Tensor:
+        """Single-rank CPU twin of the update (same math through the CPU branches of the ops)."""
+        assert self.world == 1
+        for s in self.layout.segments[0]:
+            self.grad_shard[s.shard_offset: s.shard_offset + s.numel].copy_(self.grads[s.full_offset: s.full_offset + s.numel])
+        K.sumsq(self.grad_shard, self._norm_global[0:1])
+        norm = self._norm_global[0].sqrt()
+        K.adamw_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, None, lr, betas[0], betas[1], eps, weight_decay,
+                 self.opt_step, gnorm=norm if max_norm > 0 else None, max_norm=max_norm)
+        self.publish_params()
+        self._accum = False
+        return norm
+
+    def zero_grad(self) -> None:
+        self._accum = False
+
+    def train_step(self, tokens: torch.Tensor, labels: torch.Tensor, lr: float, micro_bs: int | None = None,
+                   betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1, max_norm: float = 1.0,
+                   seq_start: torch.Tensor | None = None, sync_loss: bool = True):
+        """One optimizer step on this rank's batch ``[B, T]`` (host or device tensors).
+
+        Host tensors (pinned recommended) are copied to the device on the compute stream; the batch
+        is split into micro-batches of ``micro_bs`` sequences whose gradients accumulate; then the
+        reduce-scatter / clip / AdamW / all-gather update runs. Returns ``(loss, grad_norm)`` as
+        Python floats when ``sync_loss`` (one device-to-host read), else as device scalars."""
+        B = tokens.shape[0]
+        micro_bs = micro_bs or B
+        assert B % micro_bs == 0
+        n_micro = B // micro_bs
+        if not tokens.is_cuda and self.device.type == "cuda":
+            tokens = tokens.to(self.device, non_blocking=True)
+            labels = labels.to(self.device, non_blocking=True)
+        total = self._buf("step.loss", (2,), torch.float32)
+        total.zero_()
+        for mb in range(n_micro):
+            sl = slice(mb * micro_bs, (mb + 1) * micro_bs)
+            ss = None
+            if seq_start is not None:
+                T = tokens.shape[1]
+                ss = seq_start[mb * micro_bs * T: (mb + 1) * micro_bs * T] - mb * micro_bs * T
+            out = self.forward_backward(tokens[sl], labels[sl], seq_start=ss, loss_scale=1.0 / n_micro)
+            total[0] += out["loss"] / n_micro
+            total[1] += out["z_loss"] / n_micro
+        norm = self.optimizer_step(lr, betas, eps, weight_decay, max_norm)
+        if sync_loss:
+            host = torch.stack([total[0], total[1], norm]).tolist()   # the step's only device->host read
+            return host[0], host[2]
+        return total[0], norm
+
+    # ------------------------------------------------------------------------------------------
+    # inference-style forward (logits), used by tests and evaluation
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward_logits(self, tokens: torch.Tensor, seq_start: torch.Tensor | None = None) -> torch.Tensor:
+        a = self.args
+        B, T = tokens.shape
+        M = B * T
+        if seq_start is None:
+            seq_start = self.default_seq_start(B, T)
+        x = self._buf("L0.x", (M, a.dim))
+        K.embedding_fwd(tokens.reshape(-1), self.w["tok_embeddings.weight"], out=x)
+        for i in range(a.n_layers):
+            nxt = self._buf(f"L{i + 1}.x", (M, a.dim))
+            self._block_fwd(i, x, T, seq_start, nxt)
+            x = nxt
+        hn, _ = K.rmsnorm_fwd(x, self.w["norm.weight"], a.norm_eps)
+        return K.gemm(hn, self.w["output.weight"], out_dtype=torch.float32).reshape(B, T, -1)

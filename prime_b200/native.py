@@ -124,9 +124,26 @@ def stream_ptr(stream: torch.cuda.Stream | None = None):
     return C.c_void_p(s.cuda_stream)
 
 
+# kernels launched per successful native call (1 unless listed); used for launch accounting
+_LAUNCHES = {"pb_rmsnorm_bwd": 2, "pb_attn_bwd": 3, "pb_sum_f32": 2, "pb_sumsq": 2, "pb_zero_reduce_grads": 2}
+_launch_count = 0
+
+
 def check(rc: int, what: str) -> None:
+    global _launch_count
     if rc != 0:
         raise NativeError(f"{what} failed with code {rc}")
+    _launch_count += _LAUNCHES.get(what.split("(", 1)[0], 1)
+
+
+def launch_counter() -> int:
+    """Number of kernels of this package launched since the last reset (this process)."""
+    return _launch_count
+
+
+def launch_counter_reset() -> None:
+    global _launch_count
+    _launch_count = 0
 
 
 def cuda_loaded_path() -> Path | None:

@@ -61,6 +61,43 @@ def attention_reference(qkv: torch.Tensor, seq_start: torch.Tensor, H: int, KV: 
     return (p @ v).transpose(0, 1).reshape(M, H * hd)
 
 
+_warned_small_head = False
+
+
+def _small_head_fwd(qkv, seq_start, H, KV, hd, scale, out):
+    """Head sizes other than 64 / 128 (only the debug presets have them) have no tensor-core
+    kernel; they run the dense fp32 statement on the device."""
+    global _warned_small_head
+    if not _warned_small_head:
+        import warnings
+        warnings.warn(f"head_dim={hd} has no tcgen05 attention kernel (64 and 128 do); using dense attention")
+        _warned_small_head = True
+    M = qkv.shape[0]
+    x = qkv.float()
+    q = x[:, : H * hd].reshape(M, H, hd).transpose(0, 1)
+    k = x[:, H * hd: (H + KV) * hd].reshape(M, KV, hd).transpose(0, 1).repeat_interleave(H // KV, dim=0)
+    s = ((q @ k.transpose(1, 2)) * scale).masked_fill(~_dense_mask(seq_start)[None], float("-inf"))
+    lse2 = torch.logsumexp(s, -1) * 1.4426950408889634
+    o = attention_reference(qkv, seq_start, H, KV, hd, scale).to(qkv.dtype)
+    if out is not None:
+        out.copy_(o)
+        o = out
+    return o, lse2
+
+
+def _small_head_bwd(qkv, dout, seq_start, H, KV, hd, scale, dqkv, rope_table, seq_len):
+    with torch.enable_grad():
+        x = qkv.detach().float().requires_grad_(True)
+        ref = attention_reference(x, seq_start, H, KV, hd, scale)
+        (g,) = torch.autograd.grad(ref, x, dout.float())
+    g = g.to(torch.bfloat16).contiguous()
+    if rope_table is not None:
+        from .kernels import rope_
+        g = rope_(g, rope_table, seq_len, H + KV, hd, backward=True)
+    dqkv.copy_(g)
+    return dqkv
+
+
 def attention_fwd(qkv: torch.Tensor, seq_start: torch.Tensor, H: int, KV: int, hd: int, scale: float | None = None,
                   out: torch.Tensor | None = None):
     """Returns (o [M, H*hd] bf16/fp32, lse2 [H, M] fp32 in log2 units of the scaled scores)."""
@@ -79,6 +116,8 @@ def attention_fwd(qkv: torch.Tensor, seq_start: torch.Tensor, H: int, KV: int, h
             o = out
         return o, lse2
     assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and seq_start.dtype == torch.int32
+    if hd not in (64, 128):
+        return _small_head_fwd(qkv, seq_start, H, KV, hd, scale, out)
     if out is None:
         out = torch.empty(M, H * hd, dtype=torch.bfloat16, device=qkv.device)
     lse2 = torch.empty(H, M, dtype=torch.float32, device=qkv.device)
@@ -97,15 +136,18 @@ def attention_bwd(qkv: torch.Tensor, o: torch.Tensor, dout: torch.Tensor, lse2: 
     if dqkv is None:
         dqkv = torch.empty_like(qkv)
     if not qkv.is_cuda:
-        x = qkv.detach().float().requires_grad_(True)
-        ref = attention_reference(x, seq_start, H, KV, hd, scale)
-        (g,) = torch.autograd.grad(ref, x, dout.float())
+        with torch.enable_grad():
+            x = qkv.detach().float().requires_grad_(True)
+            ref = attention_reference(x, seq_start, H, KV, hd, scale)
+            (g,) = torch.autograd.grad(ref, x, dout.float())
         if rope_table is not None:
             from .kernels import rope_
             g = rope_(g.contiguous(), rope_table, seq_len, H + KV, hd, backward=True)
         dqkv.copy_(g.to(dqkv.dtype))
         return dqkv
     assert dout.stride(1) == 1 and o.stride(1) == 1 and dqkv.stride(1) == 1
+    if hd not in (64, 128):
+        return _small_head_bwd(qkv, dout, seq_start, H, KV, hd, scale, dqkv, rope_table, seq_len)
     dq_acc = _scratch_buf(qkv.device, "attn_dq", M * H * hd)
     D = _scratch_buf(qkv.device, "attn_D", M * H)
     check(native.cuda().pb_attn_bwd(ptr(qkv), ptr(o), ptr(dout), ptr(lse2), ptr(seq_start), ptr(dqkv), ptr(dq_acc), ptr(D),
