@@ -11,20 +11,9 @@
 //   CE / z-loss  src/zeroband/loss.py:70-87 (max-z) and :47-66 (lse^2 z-loss of the fused path)
 //   AdamW        src/zeroband/optimizers.py:25-30 (torch.optim.AdamW semantics)
 #include "common.cuh"
+#include "rmsnorm_bwd.cuh"
 
 namespace pb {
-
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
-    uint4 u = *reinterpret_cast<const uint4*>(p);
-    float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
-}
-__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
-    uint4 u;
-    u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
-    u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
-    *reinterpret_cast<uint4*>(p) = u;
-}
 
 // ----------------------------------------------------------------------------
 // RMSNorm forward: one warp per row. y = x * rstd * w ; rstd saved (fp32).
@@ -57,98 +46,6 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
             for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
             store8(yr + c, f);
         }
-    }
-}
-
-// ----------------------------------------------------------------------------
-// RMSNorm backward. One warp per row; each lane owns columns lane*8 + 256*j.
-//   xhat = x*rstd ; g = dy*w ; dx = (g - xhat * mean(g*xhat)) * rstd (+ dres)
-//   dw  += dy * xhat  (per-CTA partials in fp32, reduced by a second kernel in fixed order)
-// NCH = N / 256 column chunks per lane.
-// ----------------------------------------------------------------------------
-template <int NCH>
-__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                                          const __nv_bfloat16* __restrict__ w,
-                                                          const float* __restrict__ rstd,
-                                                          const __nv_bfloat16* __restrict__ dy,
-                                                          const __nv_bfloat16* __restrict__ dres,
-                                                          __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial,
-                                                          int M) {
-    constexpr int N = NCH * 256;
-    __shared__ float red[8][32 * 8 + 1];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int warps_per_block = blockDim.x >> 5;
-    float wv[NCH][8];
-    float dwacc[NCH][8];
-#pragma unroll
-    for (int j = 0; j < NCH; ++j) {
-        load8(w + j * 256 + lane * 8, wv[j]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
-    }
-    for (long long row = (long long)blockIdx.x * warps_per_block + warp; row < M;
-         row += (long long)gridDim.x * warps_per_block) {
-        const float r = rstd[row];
-        float xh[NCH][8], g[NCH][8];
-        float dot = 0.f;
-#pragma unroll
-        for (int j = 0; j < NCH; ++j) {
-            float dyv[8];
-            load8(x + row * N + j * 256 + lane * 8, xh[j]);
-            load8(dy + row * N + j * 256 + lane * 8, dyv);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                xh[j][i] *= r;
-                g[j][i] = dyv[i] * wv[j][i];
-                dot += g[j][i] * xh[j][i];
-                dwacc[j][i] += dyv[i] * xh[j][i];
-            }
-        }
-        dot = warp_sum(dot) * (1.f / N);
-#pragma unroll
-        for (int j = 0; j < NCH; ++j) {
-            float o[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = (g[j][i] - xh[j][i] * dot) * r;
-            if (dres) {
-                float dr[8];
-                load8(dres + row * N + j * 256 + lane * 8, dr);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] += dr[i];
-            }
-            store8(dx + row * N + j * 256 + lane * 8, o);
-        }
-    }
-    // fixed-order reduction of the per-warp dw accumulators across the CTA
-    for (int j = 0; j < NCH; ++j) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) red[warp][lane * 8 + i] = dwacc[j][i];
-        __syncthreads();
-        if (warp == 0) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float s = 0.f;
-                for (int ww = 0; ww < warps_per_block; ++ww) s += red[ww][lane * 8 + i];
-                dw_partial[(long long)blockIdx.x * N + j * 256 + lane * 8 + i] = s;
-            }
-        }
-        __syncthreads();
-    }
-}
-
-// dw[c] (+)= sum_b partial[b, c]  (fixed order); output bf16 or fp32
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, void* __restrict__ out, int nb, int N,
-                                       int out_fp32, int accumulate) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= N) return;
-    float s = 0.f;
-    for (int b = 0; b < nb; ++b) s += partial[(long long)b * N + c];
-    if (out_fp32) {
-        float* o = reinterpret_cast<float*>(out);
-        o[c] = accumulate ? o[c] + s : s;
-    } else {
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
-        o[c] = __float2bfloat16(accumulate ? __bfloat162float(o[c]) + s : s);
     }
 }
 
