@@ -234,7 +234,11 @@ class ElasticDeviceMesh:
         self.heartbeat_timeout = float(os.getenv("ZERO_BAND_EDM_HEARTBEAT_TIMEOUT_SECONDS", "10"))
         self.global_pg = SingleWorkerGroup(self.world_info.rank)
         self.mesh_count = 0
+        if enable and self.world_info.global_addr is None:
+            self._logger.warning("DiLoCo is enabled but GLOBAL_ADDR / GLOBAL_PORT are not set: running as a single worker")
+            enable = False
         self.enable = enable
+        self.live_recovery = _NullLiveRecovery()
         self._heartbeat_thread: threading.Thread | None = None
         self._sink: _BandwidthSink | None = None
         if enable:
@@ -633,6 +637,19 @@ class ElasticDeviceMesh:
         """Probe every peer's sink and return the current ping matrix (time to move 10 Tb, in s)."""
         self._measure_connectivity()
         return self.get_pings()
+
+
+class _NullLiveRecovery:
+    """Stand-in when there is no worker group (single worker)."""
+
+    def reset(self):
+        pass
+
+    def should_send_ckpt_to(self):
+        return None
+
+    def ask_for_live_ckpt(self, rank: int):
+        pass
 
 
 class LiveRecovery:

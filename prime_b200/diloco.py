@@ -40,12 +40,13 @@ def _find_first_number(s: str) -> int | None:
 
 
 def _is_engine(model) -> bool:
-    return hasattr(model, "named_master_shards")
+    """True for backends whose local shards live in one flat fp32 buffer (``.master``)."""
+    return hasattr(model, "master") and hasattr(model, "named_master_shards")
 
 
 def _named_local_shards(model):
     """(name, fp32 local shard tensor) in parameter order."""
-    if _is_engine(model):
+    if hasattr(model, "named_master_shards"):
         return list(model.named_master_shards())
     out = []
     for name, p in model.named_parameters():

@@ -1,0 +1,112 @@
+"""End-to-end training runs on CPU ranks (gloo): plain, DiLoCo across two workers with the uint8 ring,
+activation checkpointing / z-loss flags, and checkpoint save -> resume equivalence."""
+import os
+import pickle
+import subprocess
+import sys
+
+import pytest
+
+from prime_b200.utils import get_random_available_port_list
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _launch(argv, env_extra, log_path):
+    env = dict(os.environ)
+    env.update({"CUDA_VISIBLE_DEVICES": "", "WANDB_MODE": "disabled", "ZERO_BAND_LOG_LEVEL": "INFO", "OMP_NUM_THREADS": "2"})
+    env.update(env_extra)
+    f = open(log_path, "w")
+    return subprocess.Popen([sys.executable, "-m", "prime_b200.train"] + argv, cwd=ROOT, env=env, stdout=f, stderr=subprocess.STDOUT)
+
+
+def _local_env(rank, world, port):
+    return {"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "LOCAL_WORLD_SIZE": str(world),
+            "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)}
+
+
+def _run_job(tmp_path, name, n_workers, n_local, argv, timeout=420):
+    ports = get_random_available_port_list(2 + n_workers)
+    procs, logs = [], []
+    for w in range(n_workers):
+        for r in range(n_local):
+            env = _local_env(r, n_local, ports[2 + w])
+            if n_workers > 1:
+                env.update({"GLOBAL_UNIQUE_ID": str(w), "GLOBAL_ADDR": "127.0.0.1", "GLOBAL_PORT": str(ports[0]), "GLOBAL_RANK": str(w),
+                            "GLOBAL_WORLD_SIZE": str(n_workers), "ZERO_BAND_GLOBAL_PG_TIMEOUT_SECONDS": "120"})
+            log = tmp_path / f"{name}_w{w}_r{r}.log"
+            logs.append(log)
+            extra = ["--project", str(tmp_path / f"{name}_w{w}.pkl")]
+            if n_workers > 1:
+                extra += ["--data.data_rank", str(w), "--data.data_world_size", str(n_workers)]
+            procs.append(_launch(argv + extra, env, log))
+    for p, log in zip(procs, logs):
+        try:
+            rc = p.wait(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise AssertionError(f"timeout; log tail:\n{log.read_text()[-3000:]}")
+        assert rc == 0, f"{log}:\n{log.read_text()[-3000:]}"
+    out = []
+    for w in range(n_workers):
+        with open(tmp_path / f"{name}_w{w}.pkl", "rb") as f:
+            out.append(pickle.load(f))
+    return out
+
+
+BASE = ["@configs/debug/normal.toml", "--optim.total_steps", "4", "--train.micro_bs", "4", "--optim.batch_size", "8",
+        "--data.seq_length", "128"]
+
+
+def test_single_process_training(tmp_path):
+    (m,) = _run_job(tmp_path, "plain", 1, 1, BASE)
+    steps = [x for x in m if "Loss" in x]
+    assert [x["step"] for x in steps] == [1, 2, 3, 4]
+    assert all(0 < x["Loss"] < 20 for x in steps) and "grad_norm" in steps[0] and "inner_lr" in steps[0]
+    assert steps[-1]["total_tokens"] == 4 * 8 * 128
+
+
+def test_two_local_ranks_ac_zloss_no_packing(tmp_path):
+    (m,) = _run_job(tmp_path, "dp2", 1, 2, BASE + ["--train.ac_ckpt", "--optim.z_loss", "--no-data.sequence_packing"])
+    steps = [x for x in m if "Loss" in x]
+    assert len(steps) == 4 and "z_loss" in steps[0]
+
+
+@pytest.mark.parametrize("compression", ["no", "uint8"])
+def test_diloco_two_workers(tmp_path, compression):
+    argv = ["@configs/debug/diloco.toml", "--optim.total_steps", "4", "--diloco.inner_steps", "2", "--train.micro_bs", "4",
+            "--optim.batch_size", "8", "--diloco.compression", compression, "--train.log_model_hash", "--data.seq_length", "128"]
+    a, b = _run_job(tmp_path, f"diloco_{compression}", 2, 1, argv)
+    for m in (a, b):
+        inner = [x for x in m if "Loss" in x]
+        outer = [x for x in m if "outer_step" in x]
+        assert len(inner) == 4 and len(outer) == 2 and all(x["num_peers"] == 2 for x in inner)
+        assert inner[-1]["total_tokens"] == 4 * 8 * 128 * 2
+    # after every outer step all workers hold the same model and the same outer state
+    ha = [x for x in a if "outer_model_hash_outer_step" in x]
+    hb = [x for x in b if "outer_model_hash_outer_step" in x]
+    assert len(ha) == 2
+    for x, y in zip(ha, hb):
+        assert x["outer_model_hash_outer_step"] == y["outer_model_hash_outer_step"]
+        assert x["inner_model_hash_outer_step"] == y["inner_model_hash_outer_step"]
+
+
+def test_checkpoint_resume_equivalence(tmp_path):
+    ck = tmp_path / "ckpt"
+    common = ["@configs/debug/diloco.toml", "--optim.total_steps", "8", "--diloco.inner_steps", "2", "--train.micro_bs", "4",
+              "--optim.batch_size", "8", "--train.log_model_hash", "--no-data.sequence_packing", "--train.attn_fn", "math",
+              "--ckpt.path", str(ck), "--ckpt.interval", "4", "--ckpt.topk", "5", "--data.seq_length", "128"]
+    (full,) = _run_job(tmp_path, "full", 1, 1, common)
+    assert (ck / "step_4" / ".metadata").exists() and (ck / "step_4" / "__0_0.pt").exists() and (ck / "step_4" / "data" / "_0.pt").exists()
+    (res,) = _run_job(tmp_path, "resumed", 1, 1, common + ["--ckpt.resume", str(ck / "step_4")])
+    saved = next(x for x in full if x.get("step") == 4 and "inner_model_hash_save" in x)
+    resumed = next(x for x in res if "inner_model_hash_resume" in x)
+    for k in ("inner_model_hash", "inner_optimizer_hash", "outer_optimizer_hash", "outer_model_hash"):
+        assert saved[f"{k}_save"] == resumed[f"{k}_resume"], k
+    lf = {x["step"]: x for x in full if "Loss" in x}
+    lr_ = {x["step"]: x for x in res if "Loss" in x}
+    assert sorted(lr_) == [5, 6, 7, 8]
+    for s in lr_:
+        assert abs(lf[s]["Loss"] - lr_[s]["Loss"]) < 1e-3
+        assert lf[s]["inner_lr"] == lr_[s]["inner_lr"] and lf[s]["total_tokens"] == lr_[s]["total_tokens"]
