@@ -84,11 +84,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // CTA notices it within a few hundred polls and gives up too.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = globaltimer_ns();
+    // fast path: no timer reads (a %globaltimer read costs far more than a try_wait)
+#pragma unroll 1
+    for (int i = 0; i < 2048; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
     uint32_t polls = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++polls & 0xff) == 0) {
+        if ((++polls & 0x3ff) == 0) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > PB_WAIT_BUDGET_NS) {
                 *abort_flag = 1;
