@@ -128,10 +128,10 @@ class OuterOptimizerWrapper(Stateful):
                     g[k] = v
 
 
-def non_error_barrier():
+def non_error_barrier(group=None):
     try:
         if dist.is_initialized():
-            dist.barrier()
+            dist.barrier(group)
     except Exception as e:  # noqa: BLE001
         get_logger().info(f"Error in data checkpointing barrier: {e}, continuing training")
 
@@ -248,7 +248,11 @@ class CkptManager:
 
     def __init__(self, config: CkptConfig, backend, scheduler, dataloader, training_progress: TrainingProgress,
                  data_rank: int | None, diloco_offloaded_param_list: list | None = None,
-                 diloco_offloaded_optimizer: torch.optim.Optimizer | None = None, diloco=None, use_staging: bool = True):
+                 diloco_offloaded_optimizer: torch.optim.Optimizer | None = None, diloco=None, use_staging: bool = True,
+                 process_group=None, subdir: str | None = None):
+        if subdir is not None and config.path is not None:      # several workers in one job: one tree per worker
+            config = config.model_copy(update={"path": os.path.join(config.path, subdir)})
+        self.process_group = process_group
         self.config = config
         self.backend, self.scheduler, self.dataloader = backend, scheduler, dataloader
         self.training_progress, self.data_rank = training_progress, data_rank
@@ -301,7 +305,7 @@ class CkptManager:
         write_dir = os.path.join(self._staging_root, f"step_{self.training_progress.step}") if self.use_staging else step_dir
         self._save(write_dir)
         self._logger.info(f"Saved checkpoint to {write_dir} in {time.perf_counter() - t0} seconds")
-        non_error_barrier()
+        non_error_barrier(self.process_group)
         if self.world_info.local_rank == 0:
             if self.use_staging:
                 self._point_latest(write_dir)
@@ -345,13 +349,13 @@ class CkptManager:
             if quiet:
                 warnings.simplefilter("ignore")
             os.makedirs(ckpt_path, exist_ok=True)
-            dcp.save(self.states, checkpoint_id=ckpt_path)
+            dcp.save(self.states, checkpoint_id=ckpt_path, process_group=self.process_group)
             if self.diloco_offloaded_optimizer is not None:
                 with open(os.path.join(ckpt_path, f"__{self.world_info.local_rank}_0.pt"), "wb") as f:
                     torch.save({"optimizer": OuterOptimizerWrapper(self.diloco_offloaded_optimizer).state_dict()}, f)
             data_dir = os.path.join(ckpt_path, "data")
             self.save_data(data_dir, self.dataloader, self.world_info.local_rank)
-            non_error_barrier()
+            non_error_barrier(self.process_group)
             if self.config.remote_data_path is not None:
                 base = os.path.join(self.config.remote_data_path, f"data_{self.data_rank}")
                 for name in (f"step_{self.training_progress.step}", "latest"):
@@ -413,7 +417,7 @@ class CkptManager:
         files = os.listdir(resume_ckpt_path)
         if len(files) == 1 and files[0].startswith("diloco_"):      # legacy layout: one sub-folder
             resume_ckpt_path = os.path.join(resume_ckpt_path, files[0])
-        dcp.load(self.states, checkpoint_id=resume_ckpt_path)
+        dcp.load(self.states, checkpoint_id=resume_ckpt_path, process_group=self.process_group)
         if self.config.token_count is not None:
             self.training_progress.total_tokens = self.config.token_count
         self._logger.debug("sync inner model")

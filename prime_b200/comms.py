@@ -234,6 +234,10 @@ class ElasticDeviceMesh:
         self.heartbeat_timeout = float(os.getenv("ZERO_BAND_EDM_HEARTBEAT_TIMEOUT_SECONDS", "10"))
         self.global_pg = SingleWorkerGroup(self.world_info.rank)
         self.mesh_count = 0
+        self._in_job = self.world_info.workers_in_job > 1
+        if self._in_job:
+            self._init_workers_in_job(backend, enable)
+            return
         if enable and self.world_info.global_addr is None:
             self._logger.warning("DiLoCo is enabled but GLOBAL_ADDR / GLOBAL_PORT are not set: running as a single worker")
             enable = False
@@ -260,6 +264,40 @@ class ElasticDeviceMesh:
                 self.live_recovery.ask_for_live_ckpt(self.live_recovery_rank_src)
             self.global_pg.barrier().wait()
             self._logger.info(f"global_pg size : {self.global_pg.size()}, local_pg size: {self.local_pg.size()}")
+
+    # ------------------------------------------------------------------ several workers inside one launcher
+    def _init_workers_in_job(self, backend: str, enable: bool) -> None:
+        """Static worker layout inside one job on one NVSwitch domain: sub-groups of the job's NCCL
+        group; the worker group runs on this package's NVLink kernels. Membership never changes in
+        this mode (elastic join / leave is the TCP worker group's job)."""
+        wi = self.world_info
+        self.enable = False                      # no stores, no heartbeat; the methods below become no-ops
+        self.live_recovery = _NullLiveRecovery()
+        self._heartbeat_thread = None
+        self._sink = None
+        if not dist.is_initialized():
+            dist.init_process_group(backend="nccl", device_id=torch.device("cuda", wi.device_index))
+        k, per = wi.workers_in_job, wi.local_world_size
+        self.local_pg = None
+        for w in range(k):
+            g = dist.new_group([w * per + r for r in range(per)])
+            if w == wi.global_rank:
+                self.local_pg = g
+        self._worker_pg = None
+        for r in range(per):
+            g = dist.new_group([w * per + r for w in range(k)])
+            if r == wi.local_rank:
+                self._worker_pg = g
+        from torch.distributed.device_mesh import DeviceMesh
+        mine = [wi.global_rank * per + r for r in range(per)]
+        self.mesh = self.cuda_local_mesh = DeviceMesh.from_group(self.local_pg, "cuda", torch.tensor(mine))
+        self.cpu_local_mesh = None
+        if enable:
+            from .parallel.diloco_comm import NvlinkWorkerGroup
+            from .parallel.symm import SymmComm
+            self.global_pg = NvlinkWorkerGroup(SymmComm(self._worker_pg, torch.device("cuda", wi.device_index)), 1 << 20)
+        self.mesh_count = 0
+        self._logger.info(f"workers-in-job mesh: worker {wi.global_rank}/{k}, shard rank {wi.local_rank}/{per}")
 
     # ------------------------------------------------------------------ teardown
     def close(self, destroy_local: bool = True):
@@ -570,6 +608,8 @@ class ElasticDeviceMesh:
         everyone; workers that did not arrive are remembered for eviction at the next resolution and
         the barrier fails for all."""
         if not self.enable:
+            if getattr(self, "_in_job", False):
+                self.global_pg.barrier()
             return
         flag = str(flag)
         t0 = time.perf_counter()

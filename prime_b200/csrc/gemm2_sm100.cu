@@ -1,0 +1,285 @@
+// CTA-pair bf16 GEMM for sm_100a: tcgen05.mma.cta_group::2 on a 256 x 256 output tile shared by the
+// two CTAs of a thread-block cluster (two SMs of one TPC).
+//
+// Why: the single-CTA kernel (gemm_sm100.cu) moves (128 + 256) x 64 operand elements per
+// 128 x 256 x 64 MMA block, 85 FLOP per byte of shared-memory fill, and measurements put it at the
+// L2 -> SM feed limit. In the pair, each CTA loads HALF of each operand (128 rows of A, 128 rows of
+// B) and the tensor cores of both SMs read both halves: 131 FLOP per byte filled, with no cluster
+// multicast load anywhere (every CTA TMA-loads only its own tiles; the loads carry .cta_group::2
+// solely so that their completion bytes are counted on the leader CTA's mbarrier).
+//
+// Per CTA: 6 stages x (16 KB A-half + 16 KB B-half); TMEM 512 columns = two 128 x 256 fp32
+// accumulators (rows 128*rank .. of the pair's tile), so the epilogue of tile i overlaps the main
+// loop of tile i+1. Roles per CTA: warp 0 TMA producer, warp 1 TMEM owner (+ MMA issuer in the
+// leader CTA only), warps 2-5 epilogue. Cross-CTA signalling:
+//   full[s]   (leader)  <- complete_tx from both CTAs' TMA loads
+//   empty[s]  (both)    <- tcgen05.commit.cta_group::2 with a 2-CTA arrive mask
+//   tfull[a]  (both)    <- same, after the last k-block of a tile
+//   tempty[a] (leader)  <- 4 local + 4 remote (mapa) arrives from the epilogue warps
+// Every wait is bounded (status word + abort flag), both CTAs always reach the final cluster barrier.
+#include "gemm_common.cuh"
+#include <cooperative_groups.h>
+
+namespace pb {
+
+constexpr int G2_STAGES = 6;
+constexpr int G2_HALF_BYTES = 128 * BK * 2;               // 16 KB: 128 rows x 64 bf16
+constexpr int G2_STAGE_BYTES = 2 * G2_HALF_BYTES;         // per CTA
+constexpr int G2_BN = 256;
+constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion bytes land on an mbarrier that may live in the peer CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void umma2_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on the mbarrier at this shared-memory offset in both CTAs of the pair once all MMAs issued so far retire
+__device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + G2_STAGES * G2_STAGE_BYTES);
+    const uint32_t bar_full = smem_u32(bars);                     // [STAGES]   used in the leader
+    const uint32_t bar_empty = bar_full + 8 * G2_STAGES;          // [STAGES]   each CTA
+    const uint32_t bar_tfull = bar_empty + 8 * G2_STAGES;         // [2]        each CTA
+    const uint32_t bar_tempty = bar_tfull + 16;                   // [2]        used in the leader
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * G2_STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < G2_STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, 8);       // 4 epilogue warps x 2 CTAs
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc2(smem_u32(tmem_slot), 512);
+        tmem_relinquish2();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the peer's barriers exist before anything can signal them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int num_kb = (p.K + BK - 1) / BK;
+    // the leader's copies of the barriers this CTA signals remotely
+    const uint32_t lead_full = mapa_shared(bar_full, 0);
+    const uint32_t lead_tempty = mapa_shared(bar_tempty, 0);
+
+    if (warp == 0) {
+        // ------------------------- TMA producer (both CTAs) -------------------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs) {
+            const int m0 = (tile / p.tiles_n) * 256 + int(rank) * 128;     // my half of the A rows
+            const int n0 = (tile % p.tiles_n) * G2_BN + int(rank) * 128;   // my half of the B rows
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t sa = smem_base + stage * G2_STAGE_BYTES;
+                    const uint32_t sb = sa + G2_HALF_BYTES;
+                    const uint32_t fb = lead_full + 8 * stage;
+                    if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * G2_STAGE_BYTES);   // bytes of both CTAs
+                    const int k0 = kb * BK;
+                    if constexpr (!A_MN) {
+                        tma_load_2d_pair(sa, &tmA, fb, k0, m0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmA, fb, m0 + 64 * j, k0);
+                    }
+                    if constexpr (!B_MN) {
+                        tma_load_2d_pair(sb, &tmB, fb, k0, n0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sb + j * (BK * 128), &tmB, fb, n0 + 64 * j, k0);
+                    }
+                }
+                __syncwarp();
+                if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+        if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(10000);
+    } else if (warp == 1) {
+        // ------------------------- MMA issuer (leader CTA only) -------------------------
+        if (rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(256, G2_BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+            int stage = 0, local = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * G2_BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t sa = smem_base + stage * G2_STAGE_BYTES;
+                        const uint32_t sb = sa + G2_HALF_BYTES;
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            uint64_t da, db;
+                            if constexpr (!A_MN) da = umma_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+                            else                 da = umma_smem_desc(sa + k * (UMMA_K * 128), BK * 128, 1024);
+                            if constexpr (!B_MN) db = umma_smem_desc(sb + k * (UMMA_K * 2), 16, 1024);
+                            else                 db = umma_smem_desc(sb + k * (UMMA_K * 128), BK * 128, 1024);
+                            umma2_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                        umma2_commit_both(bar_empty + 8 * stage);
+                        if (kb == num_kb - 1) umma2_commit_both(bar_tfull + 8 * acc);
+                    }
+                    __syncwarp();
+                    if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ------------------------- epilogue (warps 2..5, both CTAs) -------------------------
+        const int quad = warp & 3;
+        const int row_in_half = quad * 32 + lane;
+        int local = 0;
+        bool ok = true;
+        for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs, ++local) {
+            const int acc = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            const int m0 = (tile / p.tiles_n) * 256 + int(rank) * 128;
+            const int n0 = (tile % p.tiles_n) * G2_BN;
+            ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = m0 + row_in_half;
+            const uint32_t t_row = tmem_base + acc * G2_BN + (uint32_t(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < G2_BN; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(t_row + c, v);
+                tmem_ld_wait();
+                gemm_store_chunk(p, v, row, n0 + c);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_tempty + 8 * acc);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // nobody leaves while the pair may still touch its memory
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc2(tmem_base, 512);
+    }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t st) {
+    auto kern = gemm_bf16_tcgen05_pair<A_MN, B_MN>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_BYTES) != cudaSuccess) return -20;
+        configured = true;
+    }
+    const int tiles_m = (p.M + 255) / 256;
+    p.tiles_n = (p.N + G2_BN - 1) / G2_BN;
+    p.num_tiles = tiles_m * p.tiles_n;
+    int ctas = sm_count() & ~1;
+    if (max_ctas > 0 && ctas > (max_ctas & ~1)) ctas = max_ctas & ~1;
+    if (ctas > 2 * p.num_tiles) ctas = 2 * p.num_tiles;
+    if (ctas < 2) ctas = 2;
+    kern<<<ctas, 192, G2_SMEM_BYTES, st>>>(tmA, tmB, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}
+
+}  // namespace pb
+
+// Same contract as pb_gemm_bf16; requires nothing more of the operands. Tile 256 x 256 per CTA pair.
+extern "C" int pb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
+                                 long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_fp32, int max_ctas,
+                                 int* status, void* stream) {
+    using namespace pb;
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
+    const int vec = out_fp32 ? 4 : 8;
+    if ((ldc % vec) || (R && (ldr % vec)) || (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(R) & 15)) return -2;
+    CUtensorMap tmA, tmB;
+    int rc;
+    if (!a_mn) rc = make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, 128);
+    else       rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
+    if (rc) return rc;
+    if (!b_mn) rc = make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, 128);
+    else       rc = make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
+    if (rc) return rc;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K; p.C = C; p.R = R; p.ldc = ldc; p.ldr = ldr; p.out_fp32 = out_fp32; p.status = status;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, p, max_ctas, st);
+    if (!a_mn && b_mn)  return launch_gemm_pair<false, true>(tmA, tmB, p, max_ctas, st);
+    if (a_mn && !b_mn)  return launch_gemm_pair<true, false>(tmA, tmB, p, max_ctas, st);
+    return launch_gemm_pair<true, true>(tmA, tmB, p, max_ctas, st);
+}

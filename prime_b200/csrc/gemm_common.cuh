@@ -1,0 +1,76 @@
+// Pieces shared by the single-CTA and the CTA-pair GEMM kernels: parameters, tile constants and
+// the store of one 32-column accumulator chunk (one thread = one output row).
+#pragma once
+#include "common.cuh"
+
+namespace pb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;            // 64 bf16 = 128 B = one swizzle row
+constexpr int UMMA_K = 16;
+
+struct GemmParams {
+    int M, N, K;
+    void* C;         // output, bf16 or fp32
+    const void* R;   // optional addend with the layout/dtype of C (may alias C)
+    long long ldc, ldr;
+    int out_fp32;
+    int* status;
+    int num_tiles, tiles_n;
+};
+
+// v: 32 consecutive fp32 accumulator columns of output row `row`, starting at column `col`.
+__device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, const uint32_t (&v)[32], int row, int col) {
+    if (row >= p.M || col >= p.N) return;
+    const int ncols = min(32, p.N - col);
+    if (p.out_fp32) {
+        float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+        const float* add = p.R ? reinterpret_cast<const float*>(p.R) + (long long)row * p.ldr + col : nullptr;
+        if (ncols == 32) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                if (add) {
+                    float4 a = *reinterpret_cast<const float4*>(add + j);
+                    o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = o;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols) dst[j] = __uint_as_float(v[j]) + (add ? add[j] : 0.f);
+        }
+    } else {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+        const __nv_bfloat16* add = p.R ? reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)row * p.ldr + col : nullptr;
+        if (ncols == 32) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                float f[8];
+#pragma unroll
+                for (int t = 0; t < 8; ++t) f[t] = __uint_as_float(v[j + t]);
+                if (add) {
+                    uint4 a = *reinterpret_cast<const uint4*>(add + j);
+                    float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+                    f[0] += a0.x; f[1] += a0.y; f[2] += a1.x; f[3] += a1.y;
+                    f[4] += a2.x; f[5] += a2.y; f[6] += a3.x; f[7] += a3.y;
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(dst + j) = o;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols) dst[j] = __float2bfloat16(__uint_as_float(v[j]) + (add ? __bfloat162float(add[j]) : 0.f));
+        }
+    }
+}
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                      uint32_t box_outer);
+int sm_count();
+
+}  // namespace pb

@@ -16,24 +16,10 @@
 // owns the TMEM allocation, warps 2-5 drain the accumulator (tcgen05.ld) and write C.
 // Two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
 // No cluster multicast is used: each CTA loads its own operand tiles.
-#include "common.cuh"
+#include "gemm_common.cuh"
 #include <mutex>
 
 namespace pb {
-
-constexpr int BM = 128;
-constexpr int BK = 64;            // 64 bf16 = 128 B = one swizzle row
-constexpr int UMMA_K = 16;
-
-struct GemmParams {
-    int M, N, K;
-    void* C;         // output, bf16 or fp32
-    const void* R;   // optional addend with the layout/dtype of C (may alias C)
-    long long ldc, ldr;
-    int out_fp32;
-    int* status;
-    int num_tiles, tiles_n;
-};
 
 template <int BN>
 struct GemmCfg {
@@ -191,56 +177,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 uint32_t v[32];
                 tmem_ld32(t_row + c, v);
                 tmem_ld_wait();
-                const int col = n0 + c;
-                if (row < p.M && col < p.N) {
-                    const int ncols = min(32, p.N - col);
-                    if (p.out_fp32) {
-                        float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
-                        const float* add = p.R ? reinterpret_cast<const float*>(p.R) + (long long)row * p.ldr + col : nullptr;
-                        if (ncols == 32) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                       __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                                if (add) {
-                                    float4 a = *reinterpret_cast<const float4*>(add + j);
-                                    o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
-                                }
-                                *reinterpret_cast<float4*>(dst + j) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (j < ncols) dst[j] = __uint_as_float(v[j]) + (add ? add[j] : 0.f);
-                        }
-                    } else {
-                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
-                        const __nv_bfloat16* add = p.R ? reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)row * p.ldr + col : nullptr;
-                        if (ncols == 32) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                float f[8];
-#pragma unroll
-                                for (int t = 0; t < 8; ++t) f[t] = __uint_as_float(v[j + t]);
-                                if (add) {
-                                    uint4 a = *reinterpret_cast<const uint4*>(add + j);
-                                    float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
-                                    f[0] += a0.x; f[1] += a0.y; f[2] += a1.x; f[3] += a1.y;
-                                    f[4] += a2.x; f[5] += a2.y; f[6] += a3.x; f[7] += a3.y;
-                                }
-                                uint4 o;
-                                o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-                                o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-                                *reinterpret_cast<uint4*>(dst + j) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (j < ncols)
-                                    dst[j] = __float2bfloat16(__uint_as_float(v[j]) + (add ? __bfloat162float(add[j]) : 0.f));
-                        }
-                    }
-                }
+                gemm_store_chunk(p, v, row, n0 + c);
             }
             tc_fence_before();
             __syncwarp();
@@ -292,7 +229,7 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
     return r == CUDA_SUCCESS ? 0 : -(1000 + int(r));
 }
 
-static int sm_count() {
+int sm_count() {
     static int n = 0;
     if (!n) {
         int dev = 0;

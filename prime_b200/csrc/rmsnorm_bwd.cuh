@@ -24,7 +24,7 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
 // NCH = N / 256 column chunks per lane.
 // ----------------------------------------------------------------------------
 template <int NCH>
-__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(256, (NCH <= 4 ? 2 : 1)) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
                                                           const __nv_bfloat16* __restrict__ w,
                                                           const float* __restrict__ rstd,
                                                           const __nv_bfloat16* __restrict__ dy,
@@ -33,32 +33,43 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
                                                           int M) {
     constexpr int N = NCH * 256;
     __shared__ float red[8][32 * 8 + 1];
+    __shared__ float s_w[N];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int warps_per_block = blockDim.x >> 5;
-    float wv[NCH][8];
+    for (int c = threadIdx.x; c < N; c += blockDim.x) s_w[c] = __bfloat162float(w[c]);
     float dwacc[NCH][8];
 #pragma unroll
-    for (int j = 0; j < NCH; ++j) {
-        load8(w + j * 256 + lane * 8, wv[j]);
+    for (int j = 0; j < NCH; ++j)
 #pragma unroll
         for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
-    }
+    __syncthreads();
     for (long long row = (long long)blockIdx.x * warps_per_block + warp; row < M;
          row += (long long)gridDim.x * warps_per_block) {
+        // issue every load of the row before the first use, so one memory latency covers all of them
+        uint4 ux[NCH], uy[NCH], ur[NCH];
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+            ux[j] = *reinterpret_cast<const uint4*>(x + row * N + j * 256 + lane * 8);
+            uy[j] = *reinterpret_cast<const uint4*>(dy + row * N + j * 256 + lane * 8);
+            if (dres) ur[j] = *reinterpret_cast<const uint4*>(dres + row * N + j * 256 + lane * 8);
+        }
         const float r = rstd[row];
         float xh[NCH][8], g[NCH][8];
         float dot = 0.f;
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
-            float dyv[8];
-            load8(x + row * N + j * 256 + lane * 8, xh[j]);
-            load8(dy + row * N + j * 256 + lane * 8, dyv);
+            const uint32_t wx[4] = {ux[j].x, ux[j].y, ux[j].z, ux[j].w}, wy[4] = {uy[j].x, uy[j].y, uy[j].z, uy[j].w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                xh[j][i] *= r;
-                g[j][i] = dyv[i] * wv[j][i];
-                dot += g[j][i] * xh[j][i];
-                dwacc[j][i] += dyv[i] * xh[j][i];
+            for (int i = 0; i < 4; ++i) {
+                const float2 fx = unpack_bf16x2(wx[i]), fy = unpack_bf16x2(wy[i]);
+                const int c = j * 256 + lane * 8 + 2 * i;
+                xh[j][2 * i] = fx.x * r;
+                xh[j][2 * i + 1] = fx.y * r;
+                g[j][2 * i] = fy.x * s_w[c];
+                g[j][2 * i + 1] = fy.y * s_w[c + 1];
+                dot += g[j][2 * i] * xh[j][2 * i] + g[j][2 * i + 1] * xh[j][2 * i + 1];
+                dwacc[j][2 * i] += fy.x * xh[j][2 * i];
+                dwacc[j][2 * i + 1] += fy.y * xh[j][2 * i + 1];
             }
         }
         dot = warp_sum(dot) * (1.f / N);
@@ -68,10 +79,13 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = (g[j][i] - xh[j][i] * dot) * r;
             if (dres) {
-                float dr[8];
-                load8(dres + row * N + j * 256 + lane * 8, dr);
+                const uint32_t wr[4] = {ur[j].x, ur[j].y, ur[j].z, ur[j].w};
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] += dr[i];
+                for (int i = 0; i < 4; ++i) {
+                    const float2 fr = unpack_bf16x2(wr[i]);
+                    o[2 * i] += fr.x;
+                    o[2 * i + 1] += fr.y;
+                }
             }
             store8(dx + row * N + j * 256 + lane * 8, o);
         }

@@ -459,7 +459,8 @@ def get_dataloader(tokenizer, world_size: int, rank: int, batch_size: int, data_
         loader = StatefulLoader(UniformTokenDataset(data_config.seq_length, uniform_vocab, seed=rank), batch_size)
         return PrefetchDataLoader(loader, data_config, device)
     if data_config.fake:
-        train = FakeTokenizedDataset(data_config.seq_length, TEST_VOCAB_SIZE, seed=1234 + rank)   # seeded: a resumed run replays the same stream
+        # seeded per (worker, rank): a resumed run replays the same stream and workers see different data
+        train = FakeTokenizedDataset(data_config.seq_length, TEST_VOCAB_SIZE, seed=1234 + rank + 1000 * (data_config.data_rank or 0))
     else:
         train = load_all_datasets(data_config, "train", tokenizer, rank, world_size)
     packed = SequencePackingDataSet(train, data_config.seq_length, eos_token=tokenizer.eos_token_id)

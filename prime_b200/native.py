@@ -24,6 +24,7 @@ vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 _CUDA_SIGS = {
     # name: argtypes
     "pb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp, vp],
+    "pb_gemm_bf16_pair": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, i32, i32, i32, vp, vp],
     "pb_rmsnorm_fwd": [vp, vp, vp, vp, i32, i32, f32, vp],
     "pb_rmsnorm_bwd_ctas": [],
     "pb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],

@@ -12,6 +12,10 @@ import torch
 from .. import native
 from ..native import check, ptr, stream_ptr
 
+import os as _os
+
+# PRIME_B200_GEMM=single forces the single-CTA kernel (A/B measurements); default uses the CTA-pair kernel when it fits
+_GEMM_PAIR = _os.environ.get("PRIME_B200_GEMM", "pair") != "single"
 _status: dict[int, torch.Tensor] = {}
 _scratch: dict[tuple[int, str], torch.Tensor] = {}
 
@@ -72,10 +76,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, resi
     assert out.dtype in (torch.bfloat16, torch.float32)
     if residual is not None:
         assert residual.dtype == out.dtype and residual.shape == out.shape and residual.stride(-1) == 1
+    ldr = residual.stride(0) if residual is not None else 0
+    # bn: 0 = choose; 128 / 256 = single-CTA tile width; 512 = the CTA-pair (cta_group::2) 256x256 kernel
+    use_pair = bn == 512 or (bn == 0 and _GEMM_PAIR and M >= 512 and N >= 256)
+    if use_pair:
+        rc = native.cuda().pb_gemm_bf16_pair(ptr(a), ptr(b), ptr(out), ptr(residual), M, N, K, a.stride(0), b.stride(0),
+                                             out.stride(0), ldr, int(a_mn), int(b_mn), int(out.dtype == torch.float32), max_ctas,
+                                             ptr(status_word(a.device)), stream_ptr())
+        check(rc, f"pb_gemm_bf16_pair(M={M},N={N},K={K},a_mn={a_mn},b_mn={b_mn})")
+        return out
     rc = native.cuda().pb_gemm_bf16(
-        ptr(a), ptr(b), ptr(out), ptr(residual), M, N, K, a.stride(0), b.stride(0), out.stride(0),
-        residual.stride(0) if residual is not None else 0, int(a_mn), int(b_mn),
-        int(out.dtype == torch.float32), bn, max_ctas, ptr(status_word(a.device)), stream_ptr())
+        ptr(a), ptr(b), ptr(out), ptr(residual), M, N, K, a.stride(0), b.stride(0), out.stride(0), ldr, int(a_mn), int(b_mn),
+        int(out.dtype == torch.float32), bn if bn in (128, 256) else 0, max_ctas, ptr(status_word(a.device)), stream_ptr())
     check(rc, f"pb_gemm_bf16(M={M},N={N},K={K},a_mn={a_mn},b_mn={b_mn})")
     return out
 

@@ -89,11 +89,12 @@ def train(config: Config) -> None:
         assert config.ckpt.interval % config.diloco.inner_steps == 0, \
             "ckpt interval must be a multiple of diloco inner steps as we only save at the end of an outer step"
     use_cuda = torch.cuda.is_available()
-    device = torch.device("cuda", int(os.environ.get("PRIME_DEVICE_OFFSET", "0")) + world_info.local_rank) if use_cuda \
-        else torch.device("cpu")
+    device = torch.device("cuda", world_info.device_index) if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(device)
 
+    if world_info.workers_in_job > 1 and config.data.data_rank is None:
+        config.data.data_rank, config.data.data_world_size = world_info.global_rank, world_info.workers_in_job
     with sw.record_block("Get Tokenizer"):
         tokenizer = _get_tokenizer(config)
     vocab_size = len(tokenizer) if (config.name_model != "debugmodel" or not config.data.fake) else TEST_VOCAB_SIZE
@@ -144,13 +145,17 @@ def train(config: Config) -> None:
     ckpt_manager = CkptManager(config=config.ckpt, backend=backend, scheduler=backend.lr_scheduler, dataloader=train_dataloader,
                                training_progress=training_progress, data_rank=config.data.data_rank,
                                diloco_offloaded_optimizer=diloco.outer_optimizer if diloco is not None else None,
-                               diloco_offloaded_param_list=diloco.param_list_cpu if diloco is not None else None, diloco=diloco)
+                               diloco_offloaded_param_list=diloco.param_list_cpu if diloco is not None else None, diloco=diloco,
+                               process_group=elastic_device_mesh.local_pg if world_info.workers_in_job > 1 else None,
+                               subdir=f"worker_{world_info.global_rank}" if world_info.workers_in_job > 1 else None)
     if diloco is not None and config.ckpt.path is not None:
         ckpt_manager.start_sidecar()
 
     metric_logger = None
     if world_info.rank == 0:
         cls = WandbMetricLogger if config.metric_logger_type == "wandb" else DummyMetricLogger
+        if world_info.workers_in_job > 1 and config.metric_logger_type == "dummy":
+            config.project = f"{config.project}.w{world_info.global_rank}"      # one metrics file per worker
         metric_logger = cls(project=config.project, config={"config": config.model_dump(), "world_info": world_info.json()},
                             resume=config.wandb_resume)
 
@@ -264,7 +269,7 @@ def main(argv: list[str] | None = None) -> None:
     world_info = get_world_info()
     logger = get_logger(config)
     if torch.cuda.is_available():
-        torch.cuda.set_device(int(os.environ.get("PRIME_DEVICE_OFFSET", "0")) + world_info.local_rank)
+        torch.cuda.set_device(world_info.device_index)
 
     def run():
         try:

@@ -99,6 +99,8 @@ def get_tensor_signature(a: torch.Tensor) -> str:
     if hasattr(a, "to_local"):
         a = a.to_local()
     flat = a.detach().reshape(-1)
+    if flat.is_complex():
+        flat = torch.view_as_real(flat).reshape(-1)
     if flat.numel() < TENSOR_SIG_SAMPLE_SIZE:
         sample = flat
     else:

@@ -27,6 +27,24 @@ class WorldInfo:
         self.global_port = int(e.get("GLOBAL_PORT")) if "GLOBAL_PORT" in e else None
         self.global_world_size = int(e.get("GLOBAL_WORLD_SIZE", 1))
         self.global_rank = int(e.get("GLOBAL_RANK", 0))
+        # CUDA device of this process (PRIME_DEVICE_OFFSET lets several launchers share one box
+        # without hiding GPUs from each other, which would break NVLink peer mappings)
+        self.device_index = int(e.get("PRIME_DEVICE_OFFSET", "0")) + self.local_rank
+        # Several DiLoCo workers inside ONE launcher: the job's ranks are split into
+        # `workers_in_job` consecutive groups; each group is a worker (its own ZeRO-3 group) and
+        # rank i of every worker forms one NVLink worker group.
+        self.workers_in_job = int(e.get("PRIME_B200_WORKERS_PER_JOB", "1"))
+        self.job_rank, self.job_world_size = self.rank, self.world_size
+        if self.workers_in_job > 1:
+            assert self.local_world_size % self.workers_in_job == 0, "workers must divide the ranks of the job evenly"
+            per = self.local_world_size // self.workers_in_job
+            self.global_world_size = self.workers_in_job
+            self.global_rank = self.local_rank // per
+            self.global_unique_id = str(self.global_rank)
+            self.local_world_size = per
+            self.world_size = per
+            self.local_rank = self.local_rank % per
+            self.rank = self.rank % per
 
     def __repr__(self):
         return (f"WorldInfo(world_size={self.world_size}, rank={self.rank}, local_rank={self.local_rank}, "

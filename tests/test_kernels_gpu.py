@@ -13,7 +13,7 @@ def _rel(a, b):
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (384, 512, 320), (1000, 776, 200), (4096, 1024, 4096)])
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 512])
 def test_gemm_layouts(M, N, K, a_mn, b_mn, bn):
     torch.manual_seed(0)
     dev = "cuda"
@@ -165,3 +165,24 @@ def test_sumsq_and_clip():
     assert abs(out.item() - x.double().pow(2).sum().item()) / out.item() < 1e-5
     ops.sumsq(x.bfloat16(), out, accumulate=True)
     assert abs(out.item() - 2 * x.double().pow(2).sum().item()) / out.item() < 1e-2
+
+
+@pytest.mark.parametrize("n", [1000, 1 << 20, 3_000_001])
+def test_gpu_quantizer_matches_host(n):
+    from prime_b200.compression import host
+    from prime_b200.ops.quant import dequantize_cuda, uniform_8bit_quantize_cuda
+    torch.manual_seed(0)
+    x = torch.randn(n, device="cuda") * 1e-3
+    q, lut = uniform_8bit_quantize_cuda(x)
+    deq = dequantize_cuda(q, lut)
+    assert ((deq - x).norm() / x.norm()).item() < 0.05
+    chunk = 1 << 20
+    xc = x.cpu()
+    for c in range(min(2, lut.shape[0])):
+        sl = slice(c * chunk, min(n, (c + 1) * chunk))
+        qh, luth = host.uniform_8bit_quantize(xc[sl])
+        diff = (q[sl].cpu().int() - qh.int()).abs()
+        assert diff.max() <= 1 and (diff > 0).float().mean() < 1e-3
+        assert torch.allclose(lut[c].cpu(), luth, atol=1e-6, rtol=1e-3)
+    q2, lut2 = uniform_8bit_quantize_cuda(x)     # bit-reproducible
+    assert torch.equal(q, q2) and torch.equal(lut, lut2)

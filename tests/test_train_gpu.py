@@ -91,3 +91,26 @@ def test_nvlink_uint8_allreduce_and_fused_outer_step(tmp_path):
            "--master-port", str(get_random_available_port()), os.path.join(ROOT, "tests", "multi_gpu", "diloco_nvlink.py")]
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, (r.stdout + r.stderr)[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("compression", ["uint8", "no"])
+def test_diloco_workers_inside_one_job_over_nvlink(tmp_path, compression):
+    """Two DiLoCo workers as sub-groups of one launcher; the outer step runs on the NVLink kernels."""
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    argv = ["@configs/debug/diloco.toml", "--optim.total_steps", "4", "--diloco.inner_steps", "2", "--train.micro_bs", "4",
+            "--optim.batch_size", "8", "--data.seq_length", "256", "--diloco.compression", compression, "--train.log_model_hash",
+            "--project", str(tmp_path / "m.pkl")]
+    _torchrun(n, argv, tmp_path / "job.log", extra_env={"PRIME_B200_WORKERS_PER_JOB": "2"})
+    out = []
+    for w in range(2):
+        with open(str(tmp_path / "m.pkl") + f".w{w}", "rb") as f:
+            out.append(pickle.load(f))
+    for m in out:
+        assert len([x for x in m if "Loss" in x]) == 4 and all(x["num_peers"] == 2 for x in m if "Loss" in x)
+    ha = [x for x in out[0] if "outer_model_hash_outer_step" in x]
+    hb = [x for x in out[1] if "outer_model_hash_outer_step" in x]
+    assert len(ha) == 2
+    for x, y in zip(ha, hb):
+        assert x["outer_model_hash_outer_step"] == y["outer_model_hash_outer_step"]
+        assert x["inner_model_hash_outer_step"] == y["inner_model_hash_outer_step"]
