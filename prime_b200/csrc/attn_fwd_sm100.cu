@@ -12,8 +12,8 @@
 // (owns TMEM), warps 2-5 softmax (one thread per query row: row max / sum are thread-local).
 //   S = Q K^T            -> TMEM [128 x 128] fp32
 //   P = exp2(S*c - m*c)  -> bf16 in shared memory (128B-swizzled, K-major for the PV MMA)
-//   O_j = P V            -> TMEM [128 x HD] fp32, folded into a register accumulator with the
-//                           usual online-softmax rescale
+//   O  += P V            -> TMEM [128 x HD] fp32, accumulated by the MMA across KV tiles; rows are
+//                           rescaled in TMEM only when their running maximum grows by > 2^8
 // Outputs: o[M, H*HD] bf16 and lse2[H, M] = log2-sum-exp of the scaled scores (log2 units).
 #include "common.cuh"
 
@@ -172,7 +172,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                 for (int k = 0; k < 8; ++k) {   // 128 kv rows, 16 per step
                     const uint64_t da = umma_smem_desc(sP + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
                     const uint64_t db = umma_smem_desc(vb + k * 2048, 16384, 1024);
-                    umma_f16_ss(tO, da, db, idesc_o, k ? 1u : 0u);
+                    umma_f16_ss(tO, da, db, idesc_o, (j | k) ? 1u : 0u);   // O accumulates over all kv tiles
                 }
                 umma_commit(bar_ofull);
                 umma_commit(bar_kvempty + 8 * st);
@@ -191,6 +191,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
         }
     } else {
         // ------------------------------ softmax warps ------------------------------
+        // One thread per query row. The whole 128-wide score row is pulled from TMEM in one go and
+        // stays in registers; O lives in TMEM (the PV MMA accumulates into it) and is rescaled only
+        // when a row's running maximum grows by more than 2^8 -- until then exponentials use the
+        // older maximum, which is exact after the final division by the row sum.
         const int quad = warp & 3;
         const int r = quad * 32 + lane;           // row within the tile == TMEM lane
         const int row = q0 + r;
@@ -198,10 +202,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
         const int my_start = p.seq_start[min(row, p.M - 1)];
         const int tile_last_start = p.seq_start[min(q0 + 127, p.M - 1)];
         const float c = p.scale_log2;
-        float m_run = -INFINITY, l_run = 0.f;
-        float o_acc[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+        float m_used = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kv && ok; ++j) {
             const int kv0 = (kv_lo + j) * 128;
@@ -209,92 +210,105 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            uint32_t v[4][32];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tmem_ld32(tS + lane_off + 32 * q, v[q]);
+            tmem_ld_wait();
             const bool need_mask = (kv0 + 127 > q0) || (kv0 < tile_last_start);
-            // pass 1: row max
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int cidx = 0; cidx < 128; cidx += 32) {
-                uint32_t v[32];
-                tmem_ld32(tS + lane_off + cidx, v);
-                tmem_ld_wait();
-                if (need_mask) {
+            if (need_mask) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int s = kv0 + cidx + i;
-                        if (s <= row && s >= my_start) mx = fmaxf(mx, __uint_as_float(v[i]));
+                        const int s = kv0 + 32 * q + i;
+                        if (!(s <= row && s >= my_start)) v[q][i] = 0xff800000u;      // -inf
+                        mx = fmaxf(mx, __uint_as_float(v[q][i]));
                     }
-                } else {
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                }
+                for (int q = 0; q < 4; ++q)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[q][i]));
             }
-            const float m_new = fmaxf(m_run, mx);
-            const float m_sub = (m_new == -INFINITY) ? 0.f : m_new * c;
-            const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run * c - m_sub);
-            // pass 2: probabilities -> smem (bf16, swizzled), row sum
+            const bool grow = (mx != -INFINITY) && (m_used == -INFINITY || (mx - m_used) * c > 8.f);
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = grow ? fmaxf(m_used, mx) : m_used;
+                const float alpha = (m_used == -INFINITY) ? 0.f : exp2f((m_used - m_new) * c);
+                if (j > 0) {      // O of the previous tiles exists: wait until its last PV retired, then rescale the row
+                    ok = mbar_wait(bar_ofull, (j - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int cidx = 0; cidx < HD; cidx += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tO + lane_off + cidx, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tO + lane_off + cidx, o);
+                    }
+                    tmem_st_wait();
+                }
+                l_run *= alpha;
+                m_used = m_new;
+            }
+            const float m_sub = (m_used == -INFINITY) ? 0.f : m_used * c;
             float rs = 0.f;
-#pragma unroll 1
-            for (int cidx = 0; cidx < 128; cidx += 32) {
-                uint32_t v[32];
-                tmem_ld32(tS + lane_off + cidx, v);
-                tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
                 float pv[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    float e = exp2f(__uint_as_float(v[i]) * c - m_sub);
-                    if (need_mask) {
-                        const int s = kv0 + cidx + i;
-                        if (!(s <= row && s >= my_start)) e = 0.f;
-                    }
-                    pv[i] = e;
-                    rs += e;
+                    pv[i] = exp2f(__uint_as_float(v[q][i]) * c - m_sub);      // masked entries are -inf -> 0
+                    rs += pv[i];
                 }
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
+                for (int t = 0; t < 4; ++t) {
                     uint4 u;
-                    u.x = pack_bf16x2(pv[8 * q + 0], pv[8 * q + 1]);
-                    u.y = pack_bf16x2(pv[8 * q + 2], pv[8 * q + 3]);
-                    u.z = pack_bf16x2(pv[8 * q + 4], pv[8 * q + 5]);
-                    u.w = pack_bf16x2(pv[8 * q + 6], pv[8 * q + 7]);
-                    const int chunk = (cidx >> 3) + q;          // 16-byte chunk index 0..15 along kv
+                    u.x = pack_bf16x2(pv[8 * t + 0], pv[8 * t + 1]);
+                    u.y = pack_bf16x2(pv[8 * t + 2], pv[8 * t + 3]);
+                    u.z = pack_bf16x2(pv[8 * t + 4], pv[8 * t + 5]);
+                    u.w = pack_bf16x2(pv[8 * t + 6], pv[8 * t + 7]);
+                    const int chunk = 4 * q + t;                 // 16-byte chunk index 0..15 along kv
                     const uint32_t off = (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
                     *reinterpret_cast<uint4*>(gP + off) = u;
                 }
             }
-            l_run = l_run * alpha + rs;
-            m_run = m_new;
+            l_run += rs;
             fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_pfull);
-            // fold O_j into the running accumulator
-            ok = mbar_wait(bar_ofull, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll
-            for (int cidx = 0; cidx < HD; cidx += 32) {
-                uint32_t v[32];
-                tmem_ld32(tO + lane_off + cidx, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o_acc[cidx + i] = o_acc[cidx + i] * alpha + __uint_as_float(v[i]);
-            }
-            tc_fence_before();
         }
-        if (ok && row < p.M) {
+        if (ok) {
+            ok = mbar_wait(bar_ofull, (n_kv - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = p.O + (long long)row * p.o_stride + head * HD;
 #pragma unroll
-            for (int i = 0; i < HD; i += 8) {
-                uint4 u;
-                u.x = pack_bf16x2(o_acc[i] * inv, o_acc[i + 1] * inv);
-                u.y = pack_bf16x2(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
-                u.z = pack_bf16x2(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
-                u.w = pack_bf16x2(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
-                *reinterpret_cast<uint4*>(dst + i) = u;
+            for (int cidx = 0; cidx < HD; cidx += 32) {
+                uint32_t o[32];
+                tmem_ld32(tO + lane_off + cidx, o);
+                tmem_ld_wait();
+                if (row < p.M) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 u;
+                        u.x = pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                        u.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                        u.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                        u.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + cidx + i) = u;
+                    }
+                }
             }
-            p.lse2[(long long)head * p.M + row] = (l_run > 0.f) ? (m_run * c + log2f(l_run)) : -INFINITY;
+            if (row < p.M) p.lse2[(long long)head * p.M + row] = (l_run > 0.f) ? (m_used * c + log2f(l_run)) : -INFINITY;
+            tc_fence_before();
         }
     }
 

@@ -76,9 +76,36 @@ __device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
-template <bool A_MN, bool B_MN>
+// ---- all-gather fused into the GEMM (ZeRO-3 parameter gather + first consuming GEMM) ----
+// B ([N, K] weights) exists only as per-rank row shards in symmetric memory. The epilogue warps of
+// every CTA, idle until the first accumulator completes, pull the remote rows with plain P2P loads
+// into this GPU's full-size B buffer in sub-units of GATHER_ROWS rows and bump a per-n-block counter;
+// the TMA producers wait (bounded) on the counter of the n-block they are about to load. The gather
+// of later n-blocks therefore overlaps the math of earlier tiles, and every remote byte crosses
+// NVLink exactly once. No multicast, no library call on peer memory.
+constexpr int GATHER_ROWS = 32;
+constexpr int GATHER_MAX_RANKS = 16;
+struct GatherParams {
+    int world, rank;
+    const __nv_bfloat16* shard[GATHER_MAX_RANKS];   // rank r's rows [r*rows_per_rank, ...) of B, row pitch ld
+    __nv_bfloat16* full;                            // local [N, ld] buffer the TMA map of B points at
+    long long ld;
+    int rows_per_rank;
+    int* counters;                                  // [ceil(N/256)] monotonically increasing sub-unit counts
+    int target;                                     // counter value that means "n-block complete" for this launch
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+template <bool A_MN, bool B_MN, bool GATHER>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+                       const GatherParams g) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -130,6 +157,22 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs) {
             const int m0 = (tile / p.tiles_n) * 256 + int(rank) * 128;     // my half of the A rows
             const int n0 = (tile % p.tiles_n) * G2_BN + int(rank) * 128;   // my half of the B rows
+            if constexpr (GATHER) {
+                // wait until every row of this n-block has landed in the local B buffer
+                const int* ctr = g.counters + (tile % p.tiles_n);
+                const uint64_t t0 = globaltimer_ns();
+                while (ok && ld_acquire_gpu(ctr) < g.target) {
+                    if (*abort_flag) ok = false;
+                    else if (globaltimer_ns() - t0 > PB_WAIT_BUDGET_NS) {
+                        *abort_flag = 1;
+                        if (p.status) atomicCAS(p.status, 0, PB_ERR_TIMEOUT_PEER | (int(blockIdx.x) << 8));
+                        ok = false;
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                fence_proxy_async_global();      // generic-proxy stores of the gather -> async-proxy (TMA) reads
+            }
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
                 ok = __all_sync(0xffffffffu, ok);
@@ -202,6 +245,39 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // ------------------------- epilogue (warps 2..5, both CTAs) -------------------------
         const int quad = warp & 3;
         const int row_in_half = quad * 32 + lane;
+        if constexpr (GATHER) {
+            const int et = threadIdx.x - 64;                       // 0..127 within the four epilogue warps
+            const int n_units = (p.N + GATHER_ROWS - 1) / GATHER_ROWS;
+            const int vec_per_row = p.K / 8;                       // 16-byte vectors per row (K % 8 == 0)
+            for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+                const int r0 = u * GATHER_ROWS, r1 = min(p.N, r0 + GATHER_ROWS);
+                const int owner = r0 / g.rows_per_rank;            // GATHER_ROWS divides rows_per_rank
+                if (owner != g.rank) {
+                    const __nv_bfloat16* src = g.shard[owner] + (long long)(r0 - owner * g.rows_per_rank) * g.ld;
+                    __nv_bfloat16* dst = g.full + (long long)r0 * g.ld;
+                    const int total = (r1 - r0) * vec_per_row;
+                    for (int i = et; i < total; i += 128 * 4) {    // 4 independent 16-byte peer loads in flight per thread
+                        uint4 v[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int j = i + k * 128;
+                            if (j < total) v[k] = *reinterpret_cast<const uint4*>(src + (long long)(j / vec_per_row) * g.ld + (j % vec_per_row) * 8);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int j = i + k * 128;
+                            if (j < total) *reinterpret_cast<uint4*>(dst + (long long)(j / vec_per_row) * g.ld + (j % vec_per_row) * 8) = v[k];
+                        }
+                    }
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps only
+                if (et == 0) {
+                    fence_proxy_async_global();
+                    asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(g.counters + r0 / G2_BN) : "memory");
+                }
+            }
+        }
         int local = 0;
         bool ok = true;
         for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs, ++local) {
@@ -237,9 +313,10 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
 }
 
-template <bool A_MN, bool B_MN>
-static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t st) {
-    auto kern = gemm_bf16_tcgen05_pair<A_MN, B_MN>;
+template <bool A_MN, bool B_MN, bool GATHER = false>
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t st,
+                            const GatherParams& g = GatherParams{}) {
+    auto kern = gemm_bf16_tcgen05_pair<A_MN, B_MN, GATHER>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_BYTES) != cudaSuccess) return -20;
@@ -252,7 +329,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
     if (max_ctas > 0 && ctas > (max_ctas & ~1)) ctas = max_ctas & ~1;
     if (ctas > 2 * p.num_tiles) ctas = 2 * p.num_tiles;
     if (ctas < 2) ctas = 2;
-    kern<<<ctas, 192, G2_SMEM_BYTES, st>>>(tmA, tmB, p);
+    kern<<<ctas, 192, G2_SMEM_BYTES, st>>>(tmA, tmB, p, g);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 
@@ -282,4 +359,39 @@ extern "C" int pb_gemm_bf16_pair(const void* A, const void* B, void* C, const vo
     if (!a_mn && b_mn)  return launch_gemm_pair<false, true>(tmA, tmB, p, max_ctas, st);
     if (a_mn && !b_mn)  return launch_gemm_pair<true, false>(tmA, tmB, p, max_ctas, st);
     return launch_gemm_pair<true, true>(tmA, tmB, p, max_ctas, st);
+}
+
+// All-gather fused GEMM: C[M,N] = A[M,K] * B[N,K]^T (+R) where B is row-sharded over `world` ranks.
+//   shards[r]   : rank r's rows [r*rows_per_rank, min(N,(r+1)*rows_per_rank)) of B, pitch ldb (peer pointers)
+//   b_full      : this GPU's [N, ldb] buffer; its own rows must already be in place, the rest is filled here
+//   counters    : int[ceil(N/256)], zeroed once by the caller; `call_index` (1, 2, ...) = number of gathers
+//                 run on these counters including this one (they only grow, so no reset race exists)
+// The caller must order this launch after every rank has published its shard (e.g. SymmComm.barrier()).
+// rows_per_rank must be a multiple of 32.
+extern "C" int pb_gemm_bf16_allgather(const void* A, void* const* shards, void* b_full, void* C, const void* R, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int out_fp32, int world,
+                                      int rank, int rows_per_rank, int* counters, int call_index, int max_ctas, int* status,
+                                      void* stream) {
+    using namespace pb;
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (world > GATHER_MAX_RANKS || (rows_per_rank % GATHER_ROWS) || (K % 8)) return -1;
+    if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(b_full) & 15)) return -1;
+    const int vec = out_fp32 ? 4 : 8;
+    if ((ldc % vec) || (R && (ldr % vec)) || (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(R) & 15)) return -2;
+    CUtensorMap tmA, tmB;
+    int rc = a_mn ? make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK) : make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, 128);
+    if (rc) return rc;
+    rc = make_tmap_bf16_2d(&tmB, b_full, K, N, ldb, BK, 128);
+    if (rc) return rc;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K; p.C = C; p.R = R; p.ldc = ldc; p.ldr = ldr; p.out_fp32 = out_fp32; p.status = status;
+    GatherParams g{};
+    g.world = world; g.rank = rank; g.full = reinterpret_cast<__nv_bfloat16*>(b_full); g.ld = ldb; g.rows_per_rank = rows_per_rank;
+    g.counters = counters;
+    g.target = call_index * (G2_BN / GATHER_ROWS);     // a partial last n-block still counts its real sub-units below
+    for (int r = 0; r < world; ++r) g.shard[r] = reinterpret_cast<const __nv_bfloat16*>(shards[r]);
+    if (N % G2_BN) return -3;                          // keep the per-block sub-unit count uniform
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    return a_mn ? launch_gemm_pair<true, false, true>(tmA, tmB, p, max_ctas, st, g)
+                : launch_gemm_pair<false, false, true>(tmA, tmB, p, max_ctas, st, g);
 }

@@ -114,3 +114,14 @@ def test_diloco_workers_inside_one_job_over_nvlink(tmp_path, compression):
     for x, y in zip(ha, hb):
         assert x["outer_model_hash_outer_step"] == y["outer_model_hash_outer_step"]
         assert x["inner_model_hash_outer_step"] == y["inner_model_hash_outer_step"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_allgather_fused_gemm(tmp_path):
+    n = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(get_random_available_port()), os.path.join(ROOT, "tests", "multi_gpu", "ag_gemm.py")]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-4000:]
+    print(r.stdout[-500:])
