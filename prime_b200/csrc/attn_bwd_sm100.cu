@@ -1,11 +1,14 @@
 // Flash attention backward (causal / document mask, GQA) for sm_100a on tcgen05 + TMEM + TMA.
 //
+// (320 threads: TMA warp, MMA warp, eight softmax / epilogue warps.) For head size 64 the pairs are
+// software-pipelined: the tensor core computes S/dP of pair i+1 and dV/dK/dQ of pair i-1 while the
+// softmax warps work on pair i from registers.
 // One CTA owns one 128-row KV tile of one KV head and walks every (query head of the group,
 // query tile) pair that can see it. Per pair (all MMAs are 128-row tcgen05 instructions):
 //   S  = Q K^T,  dP = dO V^T                 -> TMEM
 //   P  = exp2(S*c - lse2),  dS = P * (dP - D) -> bf16 in shared memory (softmax warps)
 //   dV += P^T dO,  dK += dS^T Q               -> TMEM accumulators kept for the whole CTA
-//   dQ  = dS K                                -> TMEM -> fp32 red.global.add into dq_acc
+//   dQ  = dS K                                -> TMEM -> shared memory -> bulk reduce-add (TMA) into dq_acc
 // D[h, m] = rowsum(dO * O) comes from a small pre-pass. dK/dV of a KV head are reduced over the
 // query heads of its group inside the CTA (no repeat_kv materialisation, no cross-CTA atomics
 // for them). The same shared-memory tile is consumed K-major by one MMA and MN-major by another
@@ -32,22 +35,21 @@ template <int HD>
 struct AttnBwdCfg {
     static constexpr int TILE_BYTES = 128 * HD * 2;
     static constexpr int PS_BYTES = 128 * 128 * 2;
-    static constexpr int STAGES = (HD == 64) ? 2 : 1;
-    static constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * STAGES) + 2 * PS_BYTES + 1024 + 256;
+    static constexpr int STAGES = (HD == 64) ? 3 : 1;
+    // HD=64: S/dP of pair it+1 are issued as soon as the softmax warps hold pair it in registers
+    static constexpr bool PIPE = (HD == 64);
+    static constexpr int DQ_STAGE_BYTES = 8 * 4096;   // one 32-row x 32-float box per softmax warp
+    static constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * STAGES) + 2 * PS_BYTES + DQ_STAGE_BYTES + 1024 + 256;
     static constexpr int T_S = 0, T_DP = 128;
     static constexpr int T_DV = 256, T_DK = 256 + HD;
     static constexpr int T_DQ = (HD == 64) ? 384 : 0;   // HD=128: dQ reuses the S columns
     static constexpr bool DQ_ALIASES_S = (HD != 64);
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
-                const AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams p) {
     using Cfg = AttnBwdCfg<HD>;
     constexpr int NB = HD / 64;
     constexpr int STAGES = Cfg::STAGES;
@@ -62,18 +64,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     const uint32_t sDS = sP + Cfg::PS_BYTES;
     uint8_t* gP = gen + (sP - base);
     uint8_t* gDS = gen + (sDS - base);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(gen + (sDS - base) + Cfg::PS_BYTES);
+    const uint32_t sDQ = sDS + Cfg::PS_BYTES;                    // [8 warps][32 rows][32 floats], 128B-swizzled
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gen + (sDQ - base) + Cfg::DQ_STAGE_BYTES);
     const uint32_t bar_kv = smem_u32(bars);
-    const uint32_t bar_qfull = bar_kv + 8;         // [2]
-    const uint32_t bar_dofull = bar_qfull + 16;    // [2]
-    const uint32_t bar_qdoempty = bar_dofull + 16; // [2]
-    const uint32_t bar_sfull = bar_qdoempty + 16;
-    const uint32_t bar_dpfull = bar_sfull + 8;
-    const uint32_t bar_pdsfull = bar_dpfull + 8;
+    const uint32_t bar_qfull = bar_kv + 8;           // [3]
+    const uint32_t bar_dofull = bar_qfull + 24;      // [3]
+    const uint32_t bar_qdoempty = bar_dofull + 24;   // [3]
+    const uint32_t bar_sdpfull = bar_qdoempty + 24;
+    const uint32_t bar_pdsfull = bar_sdpfull + 8;
     const uint32_t bar_dqfull = bar_pdsfull + 8;
     const uint32_t bar_dqempty = bar_dqfull + 8;
     const uint32_t bar_final = bar_dqempty + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    const uint32_t bar_sdpfree = bar_final + 8;      // softmax warps hold S and dP in registers
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -84,21 +87,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
 
     if (threadIdx.x == 0) {
         mbar_init(bar_kv, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < 3; ++s) {
             mbar_init(bar_qfull + 8 * s, 1);
             mbar_init(bar_dofull + 8 * s, 1);
             mbar_init(bar_qdoempty + 8 * s, 1);
         }
-        mbar_init(bar_sfull, 1);
-        mbar_init(bar_dpfull, 1);
-        mbar_init(bar_pdsfull, 4);
+        mbar_init(bar_sdpfull, 1);
+        mbar_init(bar_pdsfull, 8);
         mbar_init(bar_dqfull, 1);
-        mbar_init(bar_dqempty, 4);
+        mbar_init(bar_dqempty, 8);
         mbar_init(bar_final, 1);
+        mbar_init(bar_sdpfree, 8);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmQKV);
         tma_prefetch_desc(&tmDO);
+        tma_prefetch_desc(&tmDQ);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), 512);
@@ -173,7 +177,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                     const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
                     umma_f16_ss(tS, umma_smem_desc(q + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024), idesc_s, k ? 1u : 0u);
                 }
-                umma_commit(bar_sfull);
             }
             __syncwarp();
             ok = mbar_wait(bar_dofull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
@@ -187,7 +190,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                     const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
                     umma_f16_ss(tDP, umma_smem_desc(d + off, 16, 1024), umma_smem_desc(sV + off, 16, 1024), idesc_s, k ? 1u : 0u);
                 }
-                umma_commit(bar_dpfull);
+                umma_commit(bar_sdpfull);   // S and dP of this pair are both in TMEM
             }
             __syncwarp();
         };
@@ -196,6 +199,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         if (ok && n_it > 0) issue_s_dp(0, ok, 0);
         for (int it = 0; it < n_it && ok; ++it) {
             const int st = it % STAGES;
+            if (Cfg::PIPE && it + 1 < n_it) {
+                ok = mbar_wait(bar_sdpfree, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                issue_s_dp((it + 1) % STAGES, ok, it + 1);
+                if (!ok) break;
+            }
             ok = mbar_wait(bar_pdsfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -219,11 +229,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                 if (it == n_it - 1) umma_commit(bar_final);
             }
             __syncwarp();
-            if (it + 1 < n_it) issue_s_dp((it + 1) % STAGES, ok, it + 1);
+            if (!Cfg::PIPE && it + 1 < n_it) issue_s_dp((it + 1) % STAGES, ok, it + 1);
         }
     } else {
         // ------------------------------ softmax / dS / epilogue warps ------------------------------
+        // Eight warps: warp w reads TMEM lane quadrant w & 3 (a hardware rule) and takes column half
+        // (w - 2) >> 2 of every 128-wide row, so two warps share each query row of the tile.
         const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = quad * 32 + lane;
         const uint32_t lane_off = uint32_t(quad * 32) << 16;
         const uint32_t tS = tmem_base + Cfg::T_S + lane_off, tDP = tmem_base + Cfg::T_DP + lane_off,
@@ -231,79 +244,147 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                        tDQ = tmem_base + Cfg::T_DQ + lane_off;
         const float c = p.scale_log2;
         bool ok = true;
-        for (int it = 0; it < n_it && ok; ++it) {
+        // Per (head, query tile) pair: this thread's row constants, then its 64 S and 64 dP values in
+        // registers. With Cfg::PIPE the pair after the one being exponentiated is already in TMEM.
+        struct RowCtx {
+            float lse, Dr;
+            int row, my_start;
+            int q0, tile_last_start;
+        };
+        auto row_ctx = [&](int it) {
+            RowCtx x;
             const int hq = g * G + it / n_q;
             const int q0 = (kv_tile + it % n_q) * 128;
-            const int row = q0 + r;
-            const bool row_ok = row < p.M;
-            const float lse = row_ok ? p.lse2[(long long)hq * p.M + row] : 0.f;
-            const float Dr = row_ok ? p.D[(long long)hq * p.M + row] : 0.f;
-            const int my_start = row_ok ? p.seq_start[row] : 0;
-            const int tile_last_start = p.seq_start[min(q0 + 127, p.M - 1)];
-            const bool need_mask = (kv0 + 127 > q0) || (kv0 < tile_last_start) || (q0 + 127 >= p.M);
-            ok = mbar_wait(bar_sfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            ok = mbar_wait(bar_dpfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            x.row = q0 + r;
+            const bool row_ok = x.row < p.M;
+            x.lse = row_ok ? p.lse2[(long long)hq * p.M + x.row] : 0.f;
+            x.Dr = row_ok ? p.D[(long long)hq * p.M + x.row] : 0.f;
+            x.my_start = row_ok ? p.seq_start[x.row] : 0x7fffffff;   // a row past M sees no kv position
+            x.q0 = q0;
+            x.tile_last_start = p.seq_start[min(q0 + 127, p.M - 1)];
+            return x;
+        };
+        uint32_t sv[64], dv[64];
+        auto load_sdp = [&](int it) -> bool {
+            bool good = mbar_wait(bar_sdpfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) return false;
+            tc_fence_after();
+            tmem_ld32(tS + half * 64, *reinterpret_cast<uint32_t(*)[32]>(sv));
+            tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
+            tmem_ld32(tDP + half * 64, *reinterpret_cast<uint32_t(*)[32]>(dv));
+            tmem_ld32(tDP + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(dv + 32));
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (Cfg::PIPE && lane == 0) mbar_arrive(bar_sdpfree);
+            return true;
+        };
+        // dQ tile of one pair -> this warp's staging box in shared memory -> bulk reduce-add into the
+        // fp32 accumulator (rows past M are clipped by the tensor map)
+        const uint32_t my_dq = sDQ + (warp - 2) * 4096;
+        uint8_t* g_dq = gen + (my_dq - base);
+        auto drain_dq = [&](int it) -> bool {
+            const int dq_x = (g * G + it / n_q) * HD + half * (HD / 2);   // this warp's 32 x (HD/2) block of dq_acc
+            const int dq_y = (kv_tile + it % n_q) * 128 + quad * 32;
+            bool good = mbar_wait(bar_dqfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) return false;
             tc_fence_after();
 #pragma unroll 1
-            for (int cidx = 0; cidx < 128; cidx += 32) {
-                uint32_t sv[32], dv[32];
-                tmem_ld32(tS + cidx, sv);
-                tmem_ld32(tDP + cidx, dv);
+            for (int cidx = 0; cidx < HD / 2; cidx += 32) {
+                uint32_t v[32];
+                tmem_ld32(tDQ + half * (HD / 2) + cidx, v);
+                if (lane == 0) tma_store_wait_read<0>();   // the previous reduce has read the staging box
+                __syncwarp();
                 tmem_ld_wait();
-                float pv[32], ds[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float e = exp2f(__uint_as_float(sv[i]) * c - lse);
-                    if (need_mask) {
-                        const int s = kv0 + cidx + i;
-                        if (!(row_ok && s <= row && s >= my_start)) e = 0.f;
-                    }
-                    pv[i] = e;
-                    ds[i] = e * (__uint_as_float(dv[i]) - Dr);
+                for (int q = 0; q < 8; ++q) {
+                    float4 f;
+                    f.x = __uint_as_float(v[4 * q]) * p.scale;     f.y = __uint_as_float(v[4 * q + 1]) * p.scale;
+                    f.z = __uint_as_float(v[4 * q + 2]) * p.scale; f.w = __uint_as_float(v[4 * q + 3]) * p.scale;
+                    *reinterpret_cast<float4*>(g_dq + lane * 128 + ((q ^ (lane & 7)) << 4)) = f;
                 }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_reduce_add_2d(&tmDQ, my_dq, dq_x + cidx, dq_y);
+                    tma_store_commit();
+                }
+            }
+            if (!Cfg::PIPE) {   // pipelined: the next dQ MMA is ordered behind this warp's next P/dS arrival
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_dqempty);
+            }
+            return true;
+        };
+        RowCtx cur = {}, nxt = {};
+        if (n_it > 0) {
+            cur = row_ctx(0);
+            ok = load_sdp(0);
+        }
+        for (int it = 0; it < n_it && ok; ++it) {
+            if (it + 1 < n_it) nxt = row_ctx(it + 1);   // global loads land while this pair is exponentiated
+            // P = exp2(S*c - lse2), dS = P * (dP - D), packed to bf16 pairs in place of S and dP
+            // Exponentials are taken two at a time on packed bf16 pairs (ex2.approx.bf16x2): the result is
+            // P as the MMA will read it, and dS is formed from those same rounded values.
+            const bool need_mask = (kv0 + 127 > cur.q0) || (kv0 < cur.tile_last_start) || (cur.q0 + 127 >= p.M);
+            if (need_mask) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint4 u, w;
-                    u.x = pack_bf16x2(pv[8 * q + 0], pv[8 * q + 1]); u.y = pack_bf16x2(pv[8 * q + 2], pv[8 * q + 3]);
-                    u.z = pack_bf16x2(pv[8 * q + 4], pv[8 * q + 5]); u.w = pack_bf16x2(pv[8 * q + 6], pv[8 * q + 7]);
-                    w.x = pack_bf16x2(ds[8 * q + 0], ds[8 * q + 1]); w.y = pack_bf16x2(ds[8 * q + 2], ds[8 * q + 3]);
-                    w.z = pack_bf16x2(ds[8 * q + 4], ds[8 * q + 5]); w.w = pack_bf16x2(ds[8 * q + 6], ds[8 * q + 7]);
-                    const int chunk = (cidx >> 3) + q;
-                    const uint32_t off = (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
-                    *reinterpret_cast<uint4*>(gP + off) = u;
-                    *reinterpret_cast<uint4*>(gDS + off) = w;
+                for (int i = 0; i < 64; i += 2) {
+                    const int s0 = kv0 + half * 64 + i;
+                    float x0 = __uint_as_float(sv[i]) * c - cur.lse;
+                    float x1 = __uint_as_float(sv[i + 1]) * c - cur.lse;
+                    if (s0 > cur.row || s0 < cur.my_start) x0 = -INFINITY;
+                    if (s0 + 1 > cur.row || s0 + 1 < cur.my_start) x1 = -INFINITY;
+                    uint32_t e;
+                    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(pack_bf16x2(x0, x1)));
+                    const float d0 = __uint_as_float(e << 16) * (__uint_as_float(dv[i]) - cur.Dr);
+                    const float d1 = __uint_as_float(e & 0xffff0000u) * (__uint_as_float(dv[i + 1]) - cur.Dr);
+                    sv[i >> 1] = e;
+                    dv[i >> 1] = pack_bf16x2(d0, d1);
                 }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; i += 2) {
+                    const float x0 = __uint_as_float(sv[i]) * c - cur.lse;
+                    const float x1 = __uint_as_float(sv[i + 1]) * c - cur.lse;
+                    uint32_t e;
+                    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(pack_bf16x2(x0, x1)));
+                    const float d0 = __uint_as_float(e << 16) * (__uint_as_float(dv[i]) - cur.Dr);
+                    const float d1 = __uint_as_float(e & 0xffff0000u) * (__uint_as_float(dv[i + 1]) - cur.Dr);
+                    sv[i >> 1] = e;
+                    dv[i >> 1] = pack_bf16x2(d0, d1);
+                }
+            }
+            if (Cfg::PIPE && it > 0) {
+                // waits until the MMAs of the previous pair have read P/dS from shared memory
+                ok = drain_dq(it - 1);
+                if (!ok) break;
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int chunk = half * 8 + q;
+                const uint32_t off = (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(gP + off) = make_uint4(sv[4 * q], sv[4 * q + 1], sv[4 * q + 2], sv[4 * q + 3]);
+                *reinterpret_cast<uint4*>(gDS + off) = make_uint4(dv[4 * q], dv[4 * q + 1], dv[4 * q + 2], dv[4 * q + 3]);
             }
             fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_pdsfull);
-            // dQ tile -> global fp32 accumulator
-            ok = mbar_wait(bar_dqfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            float* dq_row = p.dq_acc + (long long)row * (p.H * HD) + hq * HD;
-#pragma unroll 1
-            for (int cidx = 0; cidx < HD; cidx += 32) {
-                uint32_t v[32];
-                tmem_ld32(tDQ + cidx, v);
-                tmem_ld_wait();
-                if (row_ok) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        red_add_v4(dq_row + cidx + i, __uint_as_float(v[i]) * p.scale, __uint_as_float(v[i + 1]) * p.scale,
-                                   __uint_as_float(v[i + 2]) * p.scale, __uint_as_float(v[i + 3]) * p.scale);
-                }
+            if (!Cfg::PIPE) {
+                ok = drain_dq(it);
+                if (!ok) break;
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_dqempty);
+            if (it + 1 < n_it) {
+                cur = nxt;
+                ok = load_sdp(it + 1);
+            }
         }
+        if (Cfg::PIPE && ok && n_it > 0) ok = drain_dq(n_it - 1);
+        if (lane == 0) tma_store_wait<0>();   // all reduce-adds of this warp have landed
         // final: dK (scaled) and dV of this kv tile -> bf16 gradient buffer
         if (ok && n_it > 0) {
             ok = mbar_wait(bar_final, 0, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
@@ -315,7 +396,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
             __nv_bfloat16* dk_row = p.dqkv + (long long)row * p.dqkv_stride + (p.H + g) * HD;
             __nv_bfloat16* dv_row = p.dqkv + (long long)row * p.dqkv_stride + (p.H + p.KV + g) * HD;
 #pragma unroll 1
-            for (int cidx = 0; cidx < HD; cidx += 32) {
+            for (int cidx = half * (HD / 2); cidx < (half + 1) * (HD / 2); cidx += 32) {
                 uint32_t a[32], b[32];
                 if (n_it > 0) {
                     tmem_ld32(tDK + cidx, a);
@@ -418,9 +499,12 @@ __global__ void attn_bwd_finish_kernel(const float* __restrict__ dq_acc, __nv_bf
 
 int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer);
+int make_tmap_f32_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                     uint32_t box_inner, uint32_t box_outer);
 
 template <int HD>
-static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t st) {
+static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tdq, const AttnBwdParams& p,
+                           cudaStream_t st) {
     using Cfg = AttnBwdCfg<HD>;
     auto kern = attn_bwd_kernel<HD>;
     static bool configured = false;
@@ -429,7 +513,7 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
         configured = true;
     }
     dim3 grid(p.n_tiles, p.KV);
-    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(tq, tdo, p);
+    kern<<<grid, 320, Cfg::SMEM_BYTES, st>>>(tq, tdo, tdq, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 
@@ -446,10 +530,12 @@ extern "C" int pb_attn_bwd(const void* qkv, const void* o, const void* dout, con
     if (H % KV) return -1;
     if ((qkv_stride % 8) || (o_stride % 8) || (do_stride % 8) || (dqkv_stride % 8)) return -2;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    CUtensorMap tq, tdo;
+    CUtensorMap tq, tdo, tdq;
     int rc = make_tmap_bf16_2d(&tq, qkv, uint64_t(H + 2 * KV) * HD, M, qkv_stride, 64, 128);
     if (rc) return rc;
     rc = make_tmap_bf16_2d(&tdo, dout, uint64_t(H) * HD, M, do_stride, 64, 128);
+    if (rc) return rc;
+    rc = make_tmap_f32_2d(&tdq, dq_acc, uint64_t(H) * HD, M, uint64_t(H) * HD, 32, 32);
     if (rc) return rc;
     if (cudaMemsetAsync(dq_acc, 0, size_t(M) * H * HD * sizeof(float), st) != cudaSuccess) return -40;
     {
@@ -461,7 +547,7 @@ extern "C" int pb_attn_bwd(const void* qkv, const void* o, const void* dout, con
     p.M = M; p.H = H; p.KV = KV; p.n_tiles = (M + 127) / 128; p.seq_start = seq_start; p.lse2 = lse2; p.D = D;
     p.dq_acc = dq_acc; p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv); p.dqkv_stride = dqkv_stride;
     p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    rc = HD == 64 ? launch_attn_bwd<64>(tq, tdo, p, st) : launch_attn_bwd<128>(tq, tdo, p, st);
+    rc = HD == 64 ? launch_attn_bwd<64>(tq, tdo, tdq, p, st) : launch_attn_bwd<128>(tq, tdo, tdq, p, st);
     if (rc) return rc;
     const long long total = (long long)M * (H + KV) * (HD / 8);
     long long blocks = (total + 255) / 256;

@@ -65,7 +65,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     const uint32_t bar_sfull = bar_kvempty + 16;
     const uint32_t bar_pfull = bar_sfull + 8;
     const uint32_t bar_ofull = bar_pfull + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    const uint32_t bar_sfree = bar_ofull + 8;    // softmax warps hold S_j in registers: S TMEM may be overwritten
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -84,6 +85,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
         mbar_init(bar_sfull, 1);
         mbar_init(bar_pfull, 4);
         mbar_init(bar_ofull, 1);
+        mbar_init(bar_sfree, 4);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tm);
@@ -159,6 +161,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
         for (int j = 0; j < n_kv && ok; ++j) {
             const int st = j & 1;
             const uint32_t ph = (j >> 1) & 1;
+            if (j + 1 < n_kv) {
+                // S_{j+1} is issued as soon as the softmax warps have pulled S_j into registers, so the
+                // tensor core computes it while they do the exponentials of tile j
+                const int st1 = (j + 1) & 1;
+                const uint32_t ph1 = ((j + 1) >> 1) & 1;
+                ok = mbar_wait(bar_sfree, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ok = mbar_wait(bar_kfull + 8 * st1, ph1, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) issue_s(st1);
+                __syncwarp();
+            }
             ok = mbar_wait(bar_pfull, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -178,16 +195,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                 umma_commit(bar_kvempty + 8 * st);
             }
             __syncwarp();
-            if (j + 1 < n_kv) {
-                const int st1 = (j + 1) & 1;
-                const uint32_t ph1 = ((j + 1) >> 1) & 1;
-                ok = mbar_wait(bar_kfull + 8 * st1, ph1, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) issue_s(st1);
-                __syncwarp();
-            }
         }
     } else {
         // ------------------------------ softmax warps ------------------------------
@@ -214,6 +221,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) tmem_ld32(tS + lane_off + 32 * q, v[q]);
             tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sfree);
             const bool need_mask = (kv0 + 127 > q0) || (kv0 < tile_last_start);
             float mx = -INFINITY;
             if (need_mask) {
@@ -255,22 +265,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                 m_used = m_new;
             }
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used * c;
+            // Exponentials are taken two at a time on packed bf16 pairs (ex2.approx.bf16x2): P is stored
+            // as bf16 anyway, and the packed form halves the load on the 16-per-clock special-function
+            // unit, which is what bounds this loop. The row sum adds the very values the MMA will read.
             float rs = 0.f;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                float pv[32];
+                uint32_t pw[16];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    pv[i] = exp2f(__uint_as_float(v[q][i]) * c - m_sub);      // masked entries are -inf -> 0
-                    rs += pv[i];
+                for (int i = 0; i < 16; ++i) {
+                    const float x0 = __uint_as_float(v[q][2 * i]) * c - m_sub;       // masked entries are -inf -> 0
+                    const float x1 = __uint_as_float(v[q][2 * i + 1]) * c - m_sub;
+                    uint32_t e;
+                    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(pack_bf16x2(x0, x1)));
+                    pw[i] = e;
+                    rs += __uint_as_float(e << 16) + __uint_as_float(e & 0xffff0000u);
                 }
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
-                    uint4 u;
-                    u.x = pack_bf16x2(pv[8 * t + 0], pv[8 * t + 1]);
-                    u.y = pack_bf16x2(pv[8 * t + 2], pv[8 * t + 3]);
-                    u.z = pack_bf16x2(pv[8 * t + 4], pv[8 * t + 5]);
-                    u.w = pack_bf16x2(pv[8 * t + 6], pv[8 * t + 7]);
+                    const uint4 u = make_uint4(pw[4 * t], pw[4 * t + 1], pw[4 * t + 2], pw[4 * t + 3]);
                     const int chunk = 4 * q + t;                 // 16-byte chunk index 0..15 along kv
                     const uint32_t off = (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
                     *reinterpret_cast<uint4*>(gP + off) = u;

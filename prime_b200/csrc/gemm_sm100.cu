@@ -229,6 +229,21 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
     return r == CUDA_SUCCESS ? 0 : -(1000 + int(r));
 }
 
+// 2-D fp32 tensor map (used as the destination of bulk reduce-adds)
+int make_tmap_f32_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                     uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return -10;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {ld * 4};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -(1000 + int(r));
+}
+
 int sm_count() {
     static int n = 0;
     if (!n) {
