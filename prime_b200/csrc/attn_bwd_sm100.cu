@@ -46,8 +46,16 @@ struct AttnBwdCfg {
     static constexpr bool DQ_ALIASES_S = (HD != 64);
 };
 
+__device__ __forceinline__ void reg_dealloc_64() { asm volatile("setmaxnreg.dec.sync.aligned.u32 64;"); }
+__device__ __forceinline__ void reg_dealloc_88() { asm volatile("setmaxnreg.dec.sync.aligned.u32 88;"); }
+__device__ __forceinline__ void reg_alloc_176() { asm volatile("setmaxnreg.inc.sync.aligned.u32 176;"); }
+
+// 512 threads in four warpgroups (register budgets are re-split with setmaxnreg):
+//   warps 0-3   : warp 0 = TMA producer, warp 1 = MMA issuer (2 and 3 only hold the warpgroup together)
+//   warps 4-11  : softmax warps; warp w reads TMEM lane quadrant w & 3 and column half (w - 4) >> 2
+//   warps 12-15 : dQ drain warps; warp w moves the 32 query rows of quadrant w & 3 to dq_acc
 template <int HD>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(512, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams p) {
     using Cfg = AttnBwdCfg<HD>;
@@ -64,19 +72,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     const uint32_t sDS = sP + Cfg::PS_BYTES;
     uint8_t* gP = gen + (sP - base);
     uint8_t* gDS = gen + (sDS - base);
-    const uint32_t sDQ = sDS + Cfg::PS_BYTES;                    // [8 warps][32 rows][32 floats], 128B-swizzled
+    const uint32_t sDQ = sDS + Cfg::PS_BYTES;                    // [4 drain warps][2 boxes][32 rows][32 floats], 128B-swizzled
     uint64_t* bars = reinterpret_cast<uint64_t*>(gen + (sDQ - base) + Cfg::DQ_STAGE_BYTES);
     const uint32_t bar_kv = smem_u32(bars);
-    const uint32_t bar_qfull = bar_kv + 8;           // [3]
-    const uint32_t bar_dofull = bar_qfull + 24;      // [3]
-    const uint32_t bar_qdoempty = bar_dofull + 24;   // [3]
-    const uint32_t bar_sdpfull = bar_qdoempty + 24;
-    const uint32_t bar_pdsfull = bar_sdpfull + 8;
-    const uint32_t bar_dqfull = bar_pdsfull + 8;
-    const uint32_t bar_dqempty = bar_dqfull + 8;
+    const uint32_t bar_qfull = bar_kv + 8;           // [3] Q and dO of a pair are in shared memory
+    const uint32_t bar_qdoempty = bar_qfull + 24;    // [3]
+    const uint32_t bar_sdpfull = bar_qdoempty + 24;  // S and dP of a pair are in TMEM
+    const uint32_t bar_sdpfree = bar_sdpfull + 8;    // softmax warps hold S and dP in registers (count 8)
+    const uint32_t bar_pdsfull = bar_sdpfree + 8;    // P and dS of a pair are in shared memory (count 8)
+    const uint32_t bar_dqfull = bar_pdsfull + 8;     // dV/dK/dQ MMAs of a pair are done: dQ readable, P/dS reusable
+    const uint32_t bar_dqempty = bar_dqfull + 8;     // drain warps have read dQ out of TMEM (count 4)
     const uint32_t bar_final = bar_dqempty + 8;
-    const uint32_t bar_sdpfree = bar_final + 8;      // softmax warps hold S and dP in registers
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,15 +96,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         mbar_init(bar_kv, 1);
         for (int s = 0; s < 3; ++s) {
             mbar_init(bar_qfull + 8 * s, 1);
-            mbar_init(bar_dofull + 8 * s, 1);
             mbar_init(bar_qdoempty + 8 * s, 1);
         }
         mbar_init(bar_sdpfull, 1);
+        mbar_init(bar_sdpfree, 8);
         mbar_init(bar_pdsfull, 8);
         mbar_init(bar_dqfull, 1);
-        mbar_init(bar_dqempty, 8);
+        mbar_init(bar_dqempty, 4);
         mbar_init(bar_final, 1);
-        mbar_init(bar_sdpfree, 8);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmQKV);
@@ -120,128 +126,181 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     const int n_q = i_hi - kv_tile + 1;
     const int n_it = n_q * G;
 
-    if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            mbar_expect_tx(bar_kv, 2 * Cfg::TILE_BYTES);
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                tma_load_2d(sK + b * 16384, &tmQKV, bar_kv, (p.H + g) * HD + 64 * b, kv0);
-                tma_load_2d(sV + b * 16384, &tmQKV, bar_kv, (p.H + p.KV + g) * HD + 64 * b, kv0);
-            }
-        }
-        bool ok = true;
-        for (int it = 0; it < n_it && ok; ++it) {
-            const int st = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1;
-            ok = mbar_wait(bar_qdoempty + 8 * st, ph ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+    if (warp < 4) {
+        reg_dealloc_64();
+        if (warp == 0) {
+            // ------------------------------ TMA producer ------------------------------
             if (lane == 0) {
-                const int hq = g * G + it / n_q;
-                const int q0 = (kv_tile + it % n_q) * 128;
-                mbar_expect_tx(bar_qfull + 8 * st, Cfg::TILE_BYTES);
+                mbar_expect_tx(bar_kv, 2 * Cfg::TILE_BYTES);
 #pragma unroll
-                for (int b = 0; b < NB; ++b)
-                    tma_load_2d(sQ + st * Cfg::TILE_BYTES + b * 16384, &tmQKV, bar_qfull + 8 * st, hq * HD + 64 * b, q0);
-                mbar_expect_tx(bar_dofull + 8 * st, Cfg::TILE_BYTES);
-#pragma unroll
-                for (int b = 0; b < NB; ++b)
-                    tma_load_2d(sDO + st * Cfg::TILE_BYTES + b * 16384, &tmDO, bar_dofull + 8 * st, hq * HD + 64 * b, q0);
+                for (int b = 0; b < NB; ++b) {
+                    tma_load_2d(sK + b * 16384, &tmQKV, bar_kv, (p.H + g) * HD + 64 * b, kv0);
+                    tma_load_2d(sV + b * 16384, &tmQKV, bar_kv, (p.H + p.KV + g) * HD + 64 * b, kv0);
+                }
             }
-            __syncwarp();
-        }
-        if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(10000);
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
-        constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-        constexpr uint32_t idesc_kv = umma_idesc_bf16(128, HD, 1, 1);   // dV, dK: both operands MN-major
-        constexpr uint32_t idesc_dq = umma_idesc_bf16(128, HD, 0, 1);
-        const uint32_t tS = tmem_base + Cfg::T_S, tDP = tmem_base + Cfg::T_DP, tDV = tmem_base + Cfg::T_DV,
-                       tDK = tmem_base + Cfg::T_DK, tDQ = tmem_base + Cfg::T_DQ;
-        auto issue_s_dp = [&](int st, bool& ok, int it) {
-            const uint32_t ph = (it / STAGES) & 1;
-            ok = mbar_wait(bar_qfull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) return;
-            if (Cfg::DQ_ALIASES_S && it > 0) {
-                ok = mbar_wait(bar_dqempty, (it - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+            bool ok = true;
+            int hq = g * G, qi = 0;
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int st = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                ok = mbar_wait(bar_qdoempty + 8 * st, ph ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (lane == 0) {
+                    const int q0 = (kv_tile + qi) * 128;
+                    mbar_expect_tx(bar_qfull + 8 * st, 2 * Cfg::TILE_BYTES);   // Q and dO land on one barrier
+#pragma unroll
+                    for (int b = 0; b < NB; ++b)
+                        tma_load_2d(sQ + st * Cfg::TILE_BYTES + b * 16384, &tmQKV, bar_qfull + 8 * st, hq * HD + 64 * b, q0);
+#pragma unroll
+                    for (int b = 0; b < NB; ++b)
+                        tma_load_2d(sDO + st * Cfg::TILE_BYTES + b * 16384, &tmDO, bar_qfull + 8 * st, hq * HD + 64 * b, q0);
+                }
+                __syncwarp();
+                if (++qi == n_q) { qi = 0; ++hq; }
+            }
+            if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(10000);
+        } else if (warp == 1) {
+            // ------------------------------ MMA issuer ------------------------------
+            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_kv = umma_idesc_bf16(128, HD, 1, 1);   // dV, dK: both operands MN-major
+            constexpr uint32_t idesc_dq = umma_idesc_bf16(128, HD, 0, 1);
+            const uint32_t tS = tmem_base + Cfg::T_S, tDP = tmem_base + Cfg::T_DP, tDV = tmem_base + Cfg::T_DV,
+                           tDK = tmem_base + Cfg::T_DK, tDQ = tmem_base + Cfg::T_DQ;
+            auto issue_s_dp = [&](int st, bool& ok, int it) {
+                const uint32_t ph = (it / STAGES) & 1;
+                ok = mbar_wait(bar_qfull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) return;
-            }
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t q = sQ + st * Cfg::TILE_BYTES;
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-                    umma_f16_ss(tS, umma_smem_desc(q + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024), idesc_s, k ? 1u : 0u);
+                if (Cfg::DQ_ALIASES_S && it > 0) {
+                    ok = mbar_wait(bar_dqempty, (it - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) return;
                 }
-            }
-            __syncwarp();
-            ok = mbar_wait(bar_dofull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t q = sQ + st * Cfg::TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < HD / 16; ++k) {
+                        const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+                        umma_f16_ss(tS, umma_smem_desc(q + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024), idesc_s, k ? 1u : 0u);
+                    }
+                    const uint32_t d = sDO + st * Cfg::TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < HD / 16; ++k) {
+                        const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+                        umma_f16_ss(tDP, umma_smem_desc(d + off, 16, 1024), umma_smem_desc(sV + off, 16, 1024), idesc_s, k ? 1u : 0u);
+                    }
+                    umma_commit(bar_sdpfull);
+                }
+                __syncwarp();
+            };
+            bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) return;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t d = sDO + st * Cfg::TILE_BYTES;
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-                    umma_f16_ss(tDP, umma_smem_desc(d + off, 16, 1024), umma_smem_desc(sV + off, 16, 1024), idesc_s, k ? 1u : 0u);
+            if (ok && n_it > 0) issue_s_dp(0, ok, 0);
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int st = it % STAGES;
+                if (Cfg::PIPE && it + 1 < n_it) {
+                    ok = mbar_wait(bar_sdpfree, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    issue_s_dp((it + 1) % STAGES, ok, it + 1);
+                    if (!ok) break;
                 }
-                umma_commit(bar_sdpfull);   // S and dP of this pair are both in TMEM
-            }
-            __syncwarp();
-        };
-        bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok && n_it > 0) issue_s_dp(0, ok, 0);
-        for (int it = 0; it < n_it && ok; ++it) {
-            const int st = it % STAGES;
-            if (Cfg::PIPE && it + 1 < n_it) {
-                ok = mbar_wait(bar_sdpfree, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                ok = mbar_wait(bar_pdsfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                issue_s_dp((it + 1) % STAGES, ok, it + 1);
-                if (!ok) break;
+                tc_fence_after();
+                const uint32_t q = sQ + st * Cfg::TILE_BYTES, d = sDO + st * Cfg::TILE_BYTES;
+                if (lane == 0) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)   // reduction over the 128 query rows
+                        umma_f16_ss(tDV, umma_smem_desc(sP + k * 2048, 16384, 1024), umma_smem_desc(d + k * 2048, 16384, 1024),
+                                    idesc_kv, (it | k) ? 1u : 0u);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        umma_f16_ss(tDK, umma_smem_desc(sDS + k * 2048, 16384, 1024), umma_smem_desc(q + k * 2048, 16384, 1024),
+                                    idesc_kv, (it | k) ? 1u : 0u);
+                }
+                __syncwarp();
+                if (!Cfg::DQ_ALIASES_S && it > 0) {   // the drain warps have read dQ of the previous pair
+                    ok = mbar_wait(bar_dqempty, (it - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                if (lane == 0) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)   // reduction over the 128 kv rows
+                        umma_f16_ss(tDQ, umma_smem_desc(sDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                                    umma_smem_desc(sK + k * 2048, 16384, 1024), idesc_dq, k ? 1u : 0u);
+                    umma_commit(bar_dqfull);
+                    umma_commit(bar_qdoempty + 8 * st);
+                    if (it == n_it - 1) umma_commit(bar_final);
+                }
+                __syncwarp();
+                if (!Cfg::PIPE && it + 1 < n_it) issue_s_dp((it + 1) % STAGES, ok, it + 1);
             }
-            ok = mbar_wait(bar_pdsfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
+        }
+    } else if (warp >= 12) {
+        reg_dealloc_88();
+        // ------------------------------ dQ drain warps ------------------------------
+        // dQ tile of one pair -> registers -> this warp's two staging boxes in shared memory -> bulk
+        // reduce-add into the fp32 accumulator (rows past M are clipped by the tensor map)
+        const int quad = warp & 3;
+        const uint32_t tDQ = tmem_base + Cfg::T_DQ + (uint32_t(quad * 32) << 16);
+        const uint32_t my_dq = sDQ + quad * 8192;
+        uint8_t* g_dq = gen + (my_dq - base);
+        bool ok = true;
+        int hq = g * G, qi = 0;
+        for (int it = 0; it < n_it && ok; ++it) {
+            ok = mbar_wait(bar_dqfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            if (lane == 0) {
-                const uint32_t q = sQ + st * Cfg::TILE_BYTES, d = sDO + st * Cfg::TILE_BYTES;
+            const int dq_y = (kv_tile + qi) * 128 + quad * 32;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 64) {
+                uint32_t v[64];
+                tmem_ld32(tDQ + c0, *reinterpret_cast<uint32_t(*)[32]>(v));
+                tmem_ld32(tDQ + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(v + 32));
+                if (lane == 0) tma_store_wait_read<0>();   // earlier reduce-adds have read the staging boxes
+                __syncwarp();
+                tmem_ld_wait();
+                if (c0 + 64 >= HD) {   // dQ of this pair is out of TMEM
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_dqempty);
+                }
 #pragma unroll
-                for (int k = 0; k < 8; ++k)   // reduction over the 128 query rows
-                    umma_f16_ss(tDV, umma_smem_desc(sP + k * 2048, 16384, 1024), umma_smem_desc(d + k * 2048, 16384, 1024),
-                                idesc_kv, (it | k) ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    umma_f16_ss(tDK, umma_smem_desc(sDS + k * 2048, 16384, 1024), umma_smem_desc(q + k * 2048, 16384, 1024),
-                                idesc_kv, (it | k) ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < 8; ++k)   // reduction over the 128 kv rows
-                    umma_f16_ss(tDQ, umma_smem_desc(sDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
-                                umma_smem_desc(sK + k * 2048, 16384, 1024), idesc_dq, k ? 1u : 0u);
-                umma_commit(bar_dqfull);
-                umma_commit(bar_qdoempty + 8 * st);
-                if (it == n_it - 1) umma_commit(bar_final);
+                for (int q = 0; q < 16; ++q) {
+                    float4 f;
+                    f.x = __uint_as_float(v[4 * q]) * p.scale;     f.y = __uint_as_float(v[4 * q + 1]) * p.scale;
+                    f.z = __uint_as_float(v[4 * q + 2]) * p.scale; f.w = __uint_as_float(v[4 * q + 3]) * p.scale;
+                    *reinterpret_cast<float4*>(g_dq + (q >> 3) * 4096 + lane * 128 + (((q & 7) ^ (lane & 7)) << 4)) = f;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_reduce_add_2d(&tmDQ, my_dq, hq * HD + c0, dq_y);
+                    tma_reduce_add_2d(&tmDQ, my_dq + 4096, hq * HD + c0 + 32, dq_y);
+                    tma_store_commit();
+                }
             }
-            __syncwarp();
-            if (!Cfg::PIPE && it + 1 < n_it) issue_s_dp((it + 1) % STAGES, ok, it + 1);
+            if (++qi == n_q) { qi = 0; ++hq; }
         }
+        if (lane == 0) tma_store_wait<0>();   // all reduce-adds of this warp have landed
     } else {
+        reg_alloc_176();
         // ------------------------------ softmax / dS / epilogue warps ------------------------------
         // Eight warps: warp w reads TMEM lane quadrant w & 3 (a hardware rule) and takes column half
-        // (w - 2) >> 2 of every 128-wide row, so two warps share each query row of the tile.
+        // (w - 4) >> 2 of every 128-wide row, so two warps share each query row of the tile.
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int half = (warp - 4) >> 2;
         const int r = quad * 32 + lane;
         const uint32_t lane_off = uint32_t(quad * 32) << 16;
         const uint32_t tS = tmem_base + Cfg::T_S + lane_off, tDP = tmem_base + Cfg::T_DP + lane_off,
-                       tDV = tmem_base + Cfg::T_DV + lane_off, tDK = tmem_base + Cfg::T_DK + lane_off,
-                       tDQ = tmem_base + Cfg::T_DQ + lane_off;
+                       tDV = tmem_base + Cfg::T_DV + lane_off, tDK = tmem_base + Cfg::T_DK + lane_off;
         const float c = p.scale_log2;
         bool ok = true;
         // Per (head, query tile) pair: this thread's row constants, then its 64 S and 64 dP values in
@@ -251,17 +310,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
             int row, my_start;
             int q0, tile_last_start;
         };
-        auto row_ctx = [&](int it) {
+        int hq_n = g * G, qi_n = 0;   // pair whose row constants are loaded next
+        auto row_ctx = [&]() {
             RowCtx x;
-            const int hq = g * G + it / n_q;
-            const int q0 = (kv_tile + it % n_q) * 128;
+            const int q0 = (kv_tile + qi_n) * 128;
             x.row = q0 + r;
             const bool row_ok = x.row < p.M;
-            x.lse = row_ok ? p.lse2[(long long)hq * p.M + x.row] : 0.f;
-            x.Dr = row_ok ? p.D[(long long)hq * p.M + x.row] : 0.f;
+            x.lse = row_ok ? p.lse2[(long long)hq_n * p.M + x.row] : 0.f;
+            x.Dr = row_ok ? p.D[(long long)hq_n * p.M + x.row] : 0.f;
             x.my_start = row_ok ? p.seq_start[x.row] : 0x7fffffff;   // a row past M sees no kv position
             x.q0 = q0;
             x.tile_last_start = p.seq_start[min(q0 + 127, p.M - 1)];
+            if (++qi_n == n_q) { qi_n = 0; ++hq_n; }
             return x;
         };
         uint32_t sv[64], dv[64];
@@ -275,58 +335,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
             tmem_ld32(tDP + half * 64, *reinterpret_cast<uint32_t(*)[32]>(dv));
             tmem_ld32(tDP + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(dv + 32));
             tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (Cfg::PIPE && lane == 0) mbar_arrive(bar_sdpfree);
-            return true;
-        };
-        // dQ tile of one pair -> this warp's staging box in shared memory -> bulk reduce-add into the
-        // fp32 accumulator (rows past M are clipped by the tensor map)
-        const uint32_t my_dq = sDQ + (warp - 2) * 4096;
-        uint8_t* g_dq = gen + (my_dq - base);
-        auto drain_dq = [&](int it) -> bool {
-            const int dq_x = (g * G + it / n_q) * HD + half * (HD / 2);   // this warp's 32 x (HD/2) block of dq_acc
-            const int dq_y = (kv_tile + it % n_q) * 128 + quad * 32;
-            bool good = mbar_wait(bar_dqfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
-            good = __all_sync(0xffffffffu, good);
-            if (!good) return false;
-            tc_fence_after();
-#pragma unroll 1
-            for (int cidx = 0; cidx < HD / 2; cidx += 32) {
-                uint32_t v[32];
-                tmem_ld32(tDQ + half * (HD / 2) + cidx, v);
-                if (lane == 0) tma_store_wait_read<0>();   // the previous reduce has read the staging box
-                __syncwarp();
-                tmem_ld_wait();
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    float4 f;
-                    f.x = __uint_as_float(v[4 * q]) * p.scale;     f.y = __uint_as_float(v[4 * q + 1]) * p.scale;
-                    f.z = __uint_as_float(v[4 * q + 2]) * p.scale; f.w = __uint_as_float(v[4 * q + 3]) * p.scale;
-                    *reinterpret_cast<float4*>(g_dq + lane * 128 + ((q ^ (lane & 7)) << 4)) = f;
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    tma_reduce_add_2d(&tmDQ, my_dq, dq_x + cidx, dq_y);
-                    tma_store_commit();
-                }
-            }
-            if (!Cfg::PIPE) {   // pipelined: the next dQ MMA is ordered behind this warp's next P/dS arrival
+            if (Cfg::PIPE) {
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_dqempty);
+                if (lane == 0) mbar_arrive(bar_sdpfree);
             }
             return true;
         };
         RowCtx cur = {}, nxt = {};
         if (n_it > 0) {
-            cur = row_ctx(0);
+            cur = row_ctx();
             ok = load_sdp(0);
         }
         for (int it = 0; it < n_it && ok; ++it) {
-            if (it + 1 < n_it) nxt = row_ctx(it + 1);   // global loads land while this pair is exponentiated
-            // P = exp2(S*c - lse2), dS = P * (dP - D), packed to bf16 pairs in place of S and dP
+            if (it + 1 < n_it) nxt = row_ctx();   // global loads land while this pair is exponentiated
             // Exponentials are taken two at a time on packed bf16 pairs (ex2.approx.bf16x2): the result is
             // P as the MMA will read it, and dS is formed from those same rounded values.
             const bool need_mask = (kv0 + 127 > cur.q0) || (kv0 < cur.tile_last_start) || (cur.q0 + 127 >= p.M);
@@ -358,9 +380,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                     dv[i >> 1] = pack_bf16x2(d0, d1);
                 }
             }
-            if (Cfg::PIPE && it > 0) {
-                // waits until the MMAs of the previous pair have read P/dS from shared memory
-                ok = drain_dq(it - 1);
+            if (it > 0) {
+                // the MMAs of the previous pair have read its P/dS out of shared memory
+                ok = mbar_wait(bar_dqfull, (it - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
 #pragma unroll
@@ -371,20 +394,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                 *reinterpret_cast<uint4*>(gDS + off) = make_uint4(dv[4 * q], dv[4 * q + 1], dv[4 * q + 2], dv[4 * q + 3]);
             }
             fence_proxy_async_smem();
-            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_pdsfull);
-            if (!Cfg::PIPE) {
-                ok = drain_dq(it);
-                if (!ok) break;
-            }
             if (it + 1 < n_it) {
                 cur = nxt;
                 ok = load_sdp(it + 1);
             }
         }
-        if (Cfg::PIPE && ok && n_it > 0) ok = drain_dq(n_it - 1);
-        if (lane == 0) tma_store_wait<0>();   // all reduce-adds of this warp have landed
         // final: dK (scaled) and dV of this kv tile -> bf16 gradient buffer
         if (ok && n_it > 0) {
             ok = mbar_wait(bar_final, 0, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
@@ -513,7 +529,7 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
         configured = true;
     }
     dim3 grid(p.n_tiles, p.KV);
-    kern<<<grid, 320, Cfg::SMEM_BYTES, st>>>(tq, tdo, tdq, p);
+    kern<<<grid, 512, Cfg::SMEM_BYTES, st>>>(tq, tdo, tdq, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 
