@@ -66,6 +66,50 @@ __device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"(mask) : "memory");
 }
+// One k-block (BK = 64 = four K-steps of 16) of the CTA-pair MMA in a single instruction sequence:
+// poll the full-barrier of the NEXT k-block, issue the four MMAs of this one, commit to the stage's
+// empty barrier (and to the accumulator-full barrier after the last k-block of a tile), and only then
+// consume the poll result. The descriptors of K-steps 1..3 differ from step 0 in the 14-bit start
+// address field only (+32 B for a K-major tile, +2048 B for an MN-major one, in 16-byte units).
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ bool umma2_kblock(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, bool accumulate,
+                                             uint32_t bar_empty, uint32_t bar_tfull, bool last_kb, uint32_t bar_next,
+                                             uint32_t parity_next, bool peek) {
+    constexpr uint32_t inc_a = A_MN ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+    constexpr uint32_t inc_b = B_MN ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+    uint32_t ready;
+    const uint16_t mask = 3;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P, Q, T, L, K;\n\t"
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+        "setp.ne.b32 K, %11, 0;\n\t"
+        "setp.ne.b32 P, 0, 0;\n\t"
+        "@K mbarrier.try_wait.parity.shared::cta.b64 P, [%9], %10;\n\t"
+        "setp.ne.b32 Q, %5, 0;\n\t"
+        "setp.eq.b32 T, 0, 0;\n\t"
+        "setp.ne.b32 L, %8, 0;\n\t"
+        "add.s64 a1, %2, %12;\n\t"
+        "add.s64 a2, a1, %12;\n\t"
+        "add.s64 a3, a2, %12;\n\t"
+        "add.s64 b1, %3, %13;\n\t"
+        "add.s64 b2, b1, %13;\n\t"
+        "add.s64 b3, b2, %13;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %4, Q;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], a1, b1, %4, T;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], a2, b2, %4, T;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], a3, b3, %4, T;\n\t"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%6], %14;\n\t"
+        "@L tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%7], %14;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ready)
+        : "r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(uint32_t(accumulate)), "r"(bar_empty), "r"(bar_tfull),
+          "r"(uint32_t(last_kb)), "r"(bar_next), "r"(parity_next), "r"(uint32_t(peek)), "l"(uint64_t(inc_a)),
+          "l"(uint64_t(inc_b)), "h"(mask)
+        : "memory");
+    return ready != 0;
+}
 __device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
 }
@@ -203,44 +247,45 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(10000);
     } else if (warp == 1) {
         // ------------------------- MMA issuer (leader CTA only) -------------------------
-        if (rank == 0) {
+        // One thread runs the whole loop. While the four MMAs of a k-block are being issued, the
+        // full-barrier of the next k-block is already being polled (its latency is hidden behind the
+        // issue instead of being paid between k-blocks).
+        if (rank == 0 && lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(256, G2_BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
             int stage = 0, local = 0;
             uint32_t phase = 0;
-            bool ok = true;
+            bool ok = true, ready = false;
+            const int my_tiles = p.num_tiles > pair ? (p.num_tiles - pair + n_pairs - 1) / n_pairs : 0;
+            const long long total_kb = (long long)my_tiles * num_kb;
+            long long done_kb = 0;
             for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs, ++local) {
                 const int acc = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
                 ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
-                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * G2_BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (lane == 0) {
-                        const uint32_t sa = smem_base + stage * G2_STAGE_BYTES;
-                        const uint32_t sb = sa + G2_HALF_BYTES;
-#pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k) {
-                            uint64_t da, db;
-                            if constexpr (!A_MN) da = umma_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
-                            else                 da = umma_smem_desc(sa + k * (UMMA_K * 128), BK * 128, 1024);
-                            if constexpr (!B_MN) db = umma_smem_desc(sb + k * (UMMA_K * 2), 16, 1024);
-                            else                 db = umma_smem_desc(sb + k * (UMMA_K * 128), BK * 128, 1024);
-                            umma2_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
-                        }
-                        umma2_commit_both(bar_empty + 8 * stage);
-                        if (kb == num_kb - 1) umma2_commit_both(bar_tfull + 8 * acc);
+                    if (!ready) {
+                        ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                        if (!ok) break;
                     }
-                    __syncwarp();
-                    if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * G2_STAGE_BYTES;
+                    const uint32_t sb = sa + G2_HALF_BYTES;
+                    const uint64_t da = A_MN ? umma_smem_desc(sa, BK * 128, 1024) : umma_smem_desc(sa, 16, 1024);
+                    const uint64_t db = B_MN ? umma_smem_desc(sb, BK * 128, 1024) : umma_smem_desc(sb, 16, 1024);
+                    const int nstage = stage + 1 == G2_STAGES ? 0 : stage + 1;
+                    const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
+                    ++done_kb;
+                    ready = umma2_kblock<A_MN, B_MN>(d_tmem, da, db, idesc, kb != 0, bar_empty + 8 * stage,
+                                                     bar_tfull + 8 * acc, kb == num_kb - 1, bar_full + 8 * nstage, nphase,
+                                                     done_kb < total_kb);
+                    stage = nstage;
+                    phase = nphase;
                 }
             }
         }
+        __syncwarp();
     } else {
         // ------------------------- epilogue (warps 2..5, both CTAs) -------------------------
         const int quad = warp & 3;
