@@ -162,85 +162,93 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
             if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(10000);
         } else if (warp == 1) {
             // ------------------------------ MMA issuer ------------------------------
-            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-            constexpr uint32_t idesc_kv = umma_idesc_bf16(128, HD, 1, 1);   // dV, dK: both operands MN-major
-            constexpr uint32_t idesc_dq = umma_idesc_bf16(128, HD, 0, 1);
-            const uint32_t tS = tmem_base + Cfg::T_S, tDP = tmem_base + Cfg::T_DP, tDV = tmem_base + Cfg::T_DV,
-                           tDK = tmem_base + Cfg::T_DK, tDQ = tmem_base + Cfg::T_DQ;
-            auto issue_s_dp = [&](int st, bool& ok, int it) {
-                const uint32_t ph = (it / STAGES) & 1;
-                ok = mbar_wait(bar_qfull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) return;
-                if (Cfg::DQ_ALIASES_S && it > 0) {
-                    ok = mbar_wait(bar_dqempty, (it - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) return;
-                }
-                tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t q = sQ + st * Cfg::TILE_BYTES;
-#pragma unroll
-                    for (int k = 0; k < HD / 16; ++k) {
-                        const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-                        umma_f16_ss(tS, umma_smem_desc(q + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024), idesc_s, k ? 1u : 0u);
+            // One thread runs the whole loop. Barriers that are certain to complete while a batch of
+            // MMAs is being issued are polled inside that batch (umma4_f16_ss_peek), so their latency
+            // is not paid between batches.
+            if (lane == 0) {
+                constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+                constexpr uint32_t idesc_kv = umma_idesc_bf16(128, HD, 1, 1);   // dV, dK: both operands MN-major
+                constexpr uint32_t idesc_dq = umma_idesc_bf16(128, HD, 0, 1);
+                const uint32_t tS = tmem_base + Cfg::T_S, tDP = tmem_base + Cfg::T_DP, tDV = tmem_base + Cfg::T_DV,
+                               tDK = tmem_base + Cfg::T_DK, tDQ = tmem_base + Cfg::T_DQ;
+                bool ok = true;
+                // S = Q K^T and dP = dO V^T of pair `it` (operands in stage st); polls (peek, par) meanwhile
+                auto issue_s_dp = [&](int st, int it, bool q_ready, uint32_t peek, uint32_t par) -> bool {
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!q_ready) {
+                        ok = mbar_wait(bar_qfull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                        if (!ok) return false;
                     }
-                    const uint32_t d = sDO + st * Cfg::TILE_BYTES;
-#pragma unroll
-                    for (int k = 0; k < HD / 16; ++k) {
-                        const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-                        umma_f16_ss(tDP, umma_smem_desc(d + off, 16, 1024), umma_smem_desc(sV + off, 16, 1024), idesc_s, k ? 1u : 0u);
+                    if (Cfg::DQ_ALIASES_S && it > 0) {
+                        ok = mbar_wait(bar_dqempty, (it - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                        if (!ok) return false;
                     }
-                    umma_commit(bar_sdpfull);
-                }
-                __syncwarp();
-            };
-            bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok && n_it > 0) issue_s_dp(0, ok, 0);
-            for (int it = 0; it < n_it && ok; ++it) {
-                const int st = it % STAGES;
-                if (Cfg::PIPE && it + 1 < n_it) {
-                    ok = mbar_wait(bar_sdpfree, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    issue_s_dp((it + 1) % STAGES, ok, it + 1);
-                    if (!ok) break;
-                }
-                ok = mbar_wait(bar_pdsfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t q = sQ + st * Cfg::TILE_BYTES, d = sDO + st * Cfg::TILE_BYTES;
-                if (lane == 0) {
-#pragma unroll
-                    for (int k = 0; k < 8; ++k)   // reduction over the 128 query rows
-                        umma_f16_ss(tDV, umma_smem_desc(sP + k * 2048, 16384, 1024), umma_smem_desc(d + k * 2048, 16384, 1024),
-                                    idesc_kv, (it | k) ? 1u : 0u);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k)
-                        umma_f16_ss(tDK, umma_smem_desc(sDS + k * 2048, 16384, 1024), umma_smem_desc(q + k * 2048, 16384, 1024),
-                                    idesc_kv, (it | k) ? 1u : 0u);
-                }
-                __syncwarp();
-                if (!Cfg::DQ_ALIASES_S && it > 0) {   // the drain warps have read dQ of the previous pair
-                    ok = mbar_wait(bar_dqempty, (it - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
                     tc_fence_after();
-                }
-                if (lane == 0) {
+                    const uint32_t q = sQ + st * Cfg::TILE_BYTES, d = sDO + st * Cfg::TILE_BYTES;
+                    uint32_t got = 0;
 #pragma unroll
-                    for (int k = 0; k < 8; ++k)   // reduction over the 128 kv rows
-                        umma_f16_ss(tDQ, umma_smem_desc(sDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
-                                    umma_smem_desc(sK + k * 2048, 16384, 1024), idesc_dq, k ? 1u : 0u);
-                    umma_commit(bar_dqfull);
-                    umma_commit(bar_qdoempty + 8 * st);
-                    if (it == n_it - 1) umma_commit(bar_final);
+                    for (int b = 0; b < NB; ++b)
+                        umma4_f16_ss_peek(tS, umma_smem_desc(q + b * 16384, 16, 1024), umma_smem_desc(sK + b * 16384, 16, 1024), 2, 2,
+                                          idesc_s, b ? 1u : 0u, 0, 0, 0, 0, 0, 0, 0);
+#pragma unroll
+                    for (int b = 0; b < NB; ++b)
+                        got |= umma4_f16_ss_peek(tDP, umma_smem_desc(d + b * 16384, 16, 1024), umma_smem_desc(sV + b * 16384, 16, 1024), 2, 2,
+                                                 idesc_s, b ? 1u : 0u, b == NB - 1 ? bar_sdpfull : 0, 0, 0,
+                                                 b == NB - 1 ? peek : 0, par, 0, 0);
+                    return got & 1;
+                };
+                ok = mbar_wait(bar_kv, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                if (ok && n_it > 0) issue_s_dp(0, 0, false, 0, 0);
+                bool sdpfree_ready = false, qnext_ready = false;
+                for (int it = 0; it < n_it && ok; ++it) {
+                    const int st = it % STAGES;
+                    bool pds_ready = false;
+                    if (Cfg::PIPE && it + 1 < n_it) {
+                        if (!sdpfree_ready) {
+                            ok = mbar_wait(bar_sdpfree, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                            if (!ok) break;
+                        }
+                        pds_ready = issue_s_dp((it + 1) % STAGES, it + 1, qnext_ready, bar_pdsfull, it & 1);
+                        if (!ok) break;
+                    }
+                    if (!pds_ready) {
+                        ok = mbar_wait(bar_pdsfull, it & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
+                        if (!ok) break;
+                    }
+                    tc_fence_after();
+                    const uint32_t q = sQ + st * Cfg::TILE_BYTES, d = sDO + st * Cfg::TILE_BYTES;
+                    const bool wait_dqe = !Cfg::DQ_ALIASES_S && it > 0;   // the drain warps have read dQ of the previous pair
+                    uint32_t got = 0;
+                    // dV += P^T dO, dK += dS^T Q: reduction over the 128 query rows, 16 per MMA
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        got |= umma4_f16_ss_peek(tDV, umma_smem_desc(sP + h * 8192, 16384, 1024), umma_smem_desc(d + h * 8192, 16384, 1024),
+                                                 128, 128, idesc_kv, (it | h) ? 1u : 0u, 0, 0, 0,
+                                                 (h == 0 && wait_dqe) ? bar_dqempty : 0, (it - 1) & 1, 0, 0);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        umma4_f16_ss_peek(tDK, umma_smem_desc(sDS + h * 8192, 16384, 1024), umma_smem_desc(q + h * 8192, 16384, 1024),
+                                          128, 128, idesc_kv, (it | h) ? 1u : 0u, 0, 0, 0, 0, 0, 0, 0);
+                    if (wait_dqe && !(got & 1)) {
+                        ok = mbar_wait(bar_dqempty, (it - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                        if (!ok) break;
+                    }
+                    if (wait_dqe) tc_fence_after();
+                    // dQ = dS K: reduction over the 128 kv rows. Meanwhile poll what the next iteration needs first.
+                    const int nx = Cfg::PIPE ? it + 2 : it + 1;            // pair whose Q/dO stage is needed next
+                    const bool peek_q = nx < n_it;
+                    const bool peek_free = Cfg::PIPE && it + 2 < n_it;
+                    got = umma4_f16_ss_peek(tDQ, umma_smem_desc(sDS, 16, 1024), umma_smem_desc(sK, 16384, 1024), 2, 128, idesc_dq, 0u,
+                                            0, 0, 0, peek_q ? bar_qfull + 8 * (nx % STAGES) : 0, (nx / STAGES) & 1,
+                                            peek_free ? bar_sdpfree : 0, (it + 1) & 1);
+                    umma4_f16_ss_peek(tDQ, umma_smem_desc(sDS + 16384, 16, 1024), umma_smem_desc(sK + 8192, 16384, 1024), 2, 128, idesc_dq,
+                                      1u, bar_dqfull, bar_qdoempty + 8 * st, it == n_it - 1 ? bar_final : 0, 0, 0, 0, 0);
+                    qnext_ready = got & 1;
+                    sdpfree_ready = got & 2;
+                    if (!Cfg::PIPE && it + 1 < n_it) issue_s_dp((it + 1) % STAGES, it + 1, qnext_ready, 0, 0);
                 }
-                __syncwarp();
-                if (!Cfg::PIPE && it + 1 < n_it) issue_s_dp((it + 1) % STAGES, ok, it + 1);
             }
+            __syncwarp();
         }
     } else if (warp >= 12) {
         reg_dealloc_88();

@@ -11,7 +11,7 @@
 // One CTA = one 128-row query tile of one head. Roles: warp 0 TMA producer, warp 1 MMA issuer
 // (owns TMEM), warps 2-5 softmax (one thread per query row: row max / sum are thread-local).
 //   S = Q K^T            -> TMEM [128 x 128] fp32
-//   P = exp2(S*c - m*c)  -> bf16 in shared memory (128B-swizzled, K-major for the PV MMA)
+//   P = exp2(S*c - m*c)  -> bf16 pairs in TMEM (tcgen05.st), read by the PV MMA as its A operand
 //   O  += P V            -> TMEM [128 x HD] fp32, accumulated by the MMA across KV tiles; rows are
 //                           rescaled in TMEM only when their running maximum grows by > 2^8
 // Outputs: o[M, H*HD] bf16 and lse2[H, M] = log2-sum-exp of the scaled scores (log2 units).
@@ -32,12 +32,13 @@ struct AttnFwdParams {
 template <int HD>
 struct AttnFwdCfg {
     static constexpr int TILE_BYTES = 128 * HD * 2;          // one Q / K / V tile
-    static constexpr int P_BYTES = 128 * 128 * 2;
     static constexpr int KV_STAGES = 2;
     // two CTAs of the HD=64 variant must fit one SM, so there is no alignment slack: the kernel
     // checks that the dynamic shared window is 1024-byte aligned and reports an error otherwise
-    static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 128;
-    static constexpr int TMEM_COLS = 256;                    // S: 128 cols, O: HD cols
+    static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 128;
+    // TMEM columns: S (fp32) 0..127, O (fp32) 128..128+HD, P (bf16 pairs, A operand of the PV MMA) next 64
+    static constexpr int T_P = 128 + HD;
+    static constexpr int TMEM_COLS = (HD == 64) ? 256 : 512;
 };
 
 template <int HD>
@@ -55,9 +56,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     const uint32_t sQ = base;
     const uint32_t sK = sQ + Cfg::TILE_BYTES;                           // [2]
     const uint32_t sV = sK + Cfg::KV_STAGES * Cfg::TILE_BYTES;           // [2]
-    const uint32_t sP = sV + Cfg::KV_STAGES * Cfg::TILE_BYTES;
-    uint8_t* gP = gen + (sP - base);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(gen + (sP - base) + Cfg::P_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gen + Cfg::TILE_BYTES * (1 + 2 * Cfg::KV_STAGES));
     const uint32_t bar_q = smem_u32(bars);
     const uint32_t bar_kfull = bar_q + 8;        // [2]
     const uint32_t bar_vfull = bar_kfull + 16;   // [2]
@@ -98,7 +97,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tS = tmem_base, tO = tmem_base + 128;
+    const uint32_t tS = tmem_base, tO = tmem_base + 128, tP = tmem_base + Cfg::T_P;
 
     // kv tile range: from the tile holding the first row's sequence start up to the diagonal
     const int first_start = p.seq_start[min(q0, p.M - 1)];
@@ -187,9 +186,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                 const uint32_t vb = sV + st * Cfg::TILE_BYTES;
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {   // 128 kv rows, 16 per step
-                    const uint64_t da = umma_smem_desc(sP + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+                    // A = P straight from tensor memory: 16 bf16 of every row = 8 columns per K-step
                     const uint64_t db = umma_smem_desc(vb + k * 2048, 16384, 1024);
-                    umma_f16_ss(tO, da, db, idesc_o, (j | k) ? 1u : 0u);   // O accumulates over all kv tiles
+                    umma_f16_ts(tO, tP + k * 8, db, idesc_o, (j | k) ? 1u : 0u);   // O accumulates over all kv tiles
                 }
                 umma_commit(bar_ofull);
                 umma_commit(bar_kvempty + 8 * st);
@@ -225,7 +224,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sfree);
             const bool need_mask = (kv0 + 127 > q0) || (kv0 < tile_last_start);
-            float mx = -INFINITY;
+            // row maximum over eight independent chains (a single chain of 128 dependent max
+            // instructions would cost their latency 128 times with only two warps per scheduler)
+            float mxp[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) mxp[t] = -INFINITY;
             if (need_mask) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
@@ -233,14 +236,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                     for (int i = 0; i < 32; ++i) {
                         const int s = kv0 + 32 * q + i;
                         if (!(s <= row && s >= my_start)) v[q][i] = 0xff800000u;      // -inf
-                        mx = fmaxf(mx, __uint_as_float(v[q][i]));
+                        mxp[i & 7] = fmaxf(mxp[i & 7], __uint_as_float(v[q][i]));
                     }
             } else {
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[q][i]));
+                    for (int i = 0; i < 32; ++i) mxp[i & 7] = fmaxf(mxp[i & 7], __uint_as_float(v[q][i]));
             }
+            const float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])), fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
+            bool o_done = (j == 0);   // PV of the previous tile has retired (P and O may be touched)
             const bool grow = (mx != -INFINITY) && (m_used == -INFINITY || (mx - m_used) * c > 8.f);
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? fmaxf(m_used, mx) : m_used;
@@ -249,6 +254,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                     ok = mbar_wait(bar_ofull, (j - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
+                    o_done = true;
                     tc_fence_after();
 #pragma unroll
                     for (int cidx = 0; cidx < HD; cidx += 32) {
@@ -265,10 +271,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                 m_used = m_new;
             }
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used * c;
+            if (!o_done) {   // the PV MMA of the previous tile still reads P from tensor memory until it retires
+                ok = mbar_wait(bar_ofull, (j - 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+            }
             // Exponentials are taken two at a time on packed bf16 pairs (ex2.approx.bf16x2): P is stored
             // as bf16 anyway, and the packed form halves the load on the 16-per-clock special-function
             // unit, which is what bounds this loop. The row sum adds the very values the MMA will read.
-            float rs = 0.f;
+            float rsp[8];   // eight independent partial row sums, for the same reason
+#pragma unroll
+            for (int t = 0; t < 8; ++t) rsp[t] = 0.f;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint32_t pw[16];
@@ -279,18 +293,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                     uint32_t e;
                     asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(pack_bf16x2(x0, x1)));
                     pw[i] = e;
-                    rs += __uint_as_float(e << 16) + __uint_as_float(e & 0xffff0000u);
+                    rsp[i & 7] += __uint_as_float(e << 16) + __uint_as_float(e & 0xffff0000u);
                 }
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const uint4 u = make_uint4(pw[4 * t], pw[4 * t + 1], pw[4 * t + 2], pw[4 * t + 3]);
-                    const int chunk = 4 * q + t;                 // 16-byte chunk index 0..15 along kv
-                    const uint32_t off = (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
-                    *reinterpret_cast<uint4*>(gP + off) = u;
-                }
+                tmem_st16(tP + lane_off + 16 * q, pw);   // 32 kv columns = 16 packed words of this row
             }
-            l_run += rs;
-            fence_proxy_async_smem();
+            l_run += ((rsp[0] + rsp[1]) + (rsp[2] + rsp[3])) + ((rsp[4] + rsp[5]) + (rsp[6] + rsp[7]));
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_pfull);

@@ -202,6 +202,102 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Four tcgen05.mma (cta_group::1, kind::f16, both operands in shared memory) in one instruction
+// sequence. K-steps 1..3 use the descriptors of step 0 advanced by inc_a / inc_b in the 14-bit start
+// address field (16-byte units). Up to two mbarriers are polled BEFORE the MMAs are issued and the
+// poll results are consumed only AFTER them (and after the optional commits), so the latency of the
+// polls is hidden behind the issue. A barrier address of 0 skips that commit / poll.
+// Returns bit 0 / bit 1 = phase `par0` / `par1` of `peek0` / `peek1` has completed.
+__device__ __forceinline__ uint32_t umma4_f16_ss_peek(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t inc_a,
+                                                      uint32_t inc_b, uint32_t idesc, uint32_t acc_first,
+                                                      uint32_t commit0, uint32_t commit1, uint32_t commit2,
+                                                      uint32_t peek0, uint32_t par0, uint32_t peek1, uint32_t par1) {
+    uint32_t r0, r1;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P0, P1, K0, K1, Q, T, C0, C1, C2;\n\t"
+        ".reg .b64 a1, a2, a3, b1, b2, b3, ia, ib;\n\t"
+        "setp.ne.b32 K0, %13, 0;\n\t"
+        "setp.ne.b32 K1, %15, 0;\n\t"
+        "setp.ne.b32 P0, 0, 0;\n\t"
+        "setp.ne.b32 P1, 0, 0;\n\t"
+        "@K0 mbarrier.try_wait.parity.shared::cta.b64 P0, [%13], %14;\n\t"
+        "@K1 mbarrier.try_wait.parity.shared::cta.b64 P1, [%15], %16;\n\t"
+        "setp.ne.b32 Q, %8, 0;\n\t"
+        "setp.eq.b32 T, 0, 0;\n\t"
+        "setp.ne.b32 C0, %10, 0;\n\t"
+        "setp.ne.b32 C1, %11, 0;\n\t"
+        "setp.ne.b32 C2, %12, 0;\n\t"
+        "cvt.u64.u32 ia, %5;\n\t"
+        "cvt.u64.u32 ib, %6;\n\t"
+        "add.s64 a1, %3, ia;\n\t"
+        "add.s64 a2, a1, ia;\n\t"
+        "add.s64 a3, a2, ia;\n\t"
+        "add.s64 b1, %4, ib;\n\t"
+        "add.s64 b2, b1, ib;\n\t"
+        "add.s64 b3, b2, ib;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], %3, %4, %7, Q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], a1, b1, %7, T;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], a2, b2, %7, T;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], a3, b3, %7, T;\n\t"
+        "@C0 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%10];\n\t"
+        "@C1 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%11];\n\t"
+        "@C2 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%12];\n\t"
+        "selp.u32 %0, 1, 0, P0;\n\t"
+        "selp.u32 %1, 2, 0, P1;\n\t"
+        "}\n"
+        : "=r"(r0), "=r"(r1)
+        : "r"(d_tmem), "l"(da), "l"(db), "r"(inc_a), "r"(inc_b), "r"(idesc), "r"(acc_first), "r"(0u), "r"(commit0),
+          "r"(commit1), "r"(commit2), "r"(peek0), "r"(par0), "r"(peek1), "r"(par1)
+        : "memory");
+    return r0 | r1;
+}
+// Same as umma4_f16_ss_peek with the A operand in tensor memory (its address advances by inc_a
+// columns per K-step).
+__device__ __forceinline__ uint32_t umma4_f16_ts_peek(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t inc_a,
+                                                      uint32_t inc_b, uint32_t idesc, uint32_t acc_first,
+                                                      uint32_t commit0, uint32_t commit1, uint32_t commit2,
+                                                      uint32_t peek0, uint32_t par0, uint32_t peek1, uint32_t par1) {
+    uint32_t r0, r1;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P0, P1, K0, K1, Q, T, C0, C1, C2;\n\t"
+        ".reg .b64 b1, b2, b3, ib;\n\t"
+        ".reg .b32 a1, a2, a3;\n\t"
+        "setp.ne.b32 K0, %13, 0;\n\t"
+        "setp.ne.b32 K1, %15, 0;\n\t"
+        "setp.ne.b32 P0, 0, 0;\n\t"
+        "setp.ne.b32 P1, 0, 0;\n\t"
+        "@K0 mbarrier.try_wait.parity.shared::cta.b64 P0, [%13], %14;\n\t"
+        "@K1 mbarrier.try_wait.parity.shared::cta.b64 P1, [%15], %16;\n\t"
+        "setp.ne.b32 Q, %8, 0;\n\t"
+        "setp.eq.b32 T, 0, 0;\n\t"
+        "setp.ne.b32 C0, %10, 0;\n\t"
+        "setp.ne.b32 C1, %11, 0;\n\t"
+        "setp.ne.b32 C2, %12, 0;\n\t"
+        "cvt.u64.u32 ib, %6;\n\t"
+        "add.u32 a1, %3, %5;\n\t"
+        "add.u32 a2, a1, %5;\n\t"
+        "add.u32 a3, a2, %5;\n\t"
+        "add.s64 b1, %4, ib;\n\t"
+        "add.s64 b2, b1, ib;\n\t"
+        "add.s64 b3, b2, ib;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], [%3], %4, %7, Q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], [a1], b1, %7, T;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], [a2], b2, %7, T;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], [a3], b3, %7, T;\n\t"
+        "@C0 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%10];\n\t"
+        "@C1 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%11];\n\t"
+        "@C2 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%12];\n\t"
+        "selp.u32 %0, 1, 0, P0;\n\t"
+        "selp.u32 %1, 2, 0, P1;\n\t"
+        "}\n"
+        : "=r"(r0), "=r"(r1)
+        : "r"(d_tmem), "r"(a_tmem), "l"(db), "r"(inc_a), "r"(inc_b), "r"(idesc), "r"(acc_first), "r"(0u), "r"(commit0),
+          "r"(commit1), "r"(commit2), "r"(peek0), "r"(par0), "r"(peek1), "r"(par1)
+        : "memory");
+    return r0 | r1;
+}
 // mbarrier arrives once all previously issued MMAs of this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -242,6 +338,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
           "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
           "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+          "r"(r[14]), "r"(r[15])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
