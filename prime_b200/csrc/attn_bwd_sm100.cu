@@ -458,22 +458,47 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     }
 }
 
-// D[h, m] = sum_d dO[m, h*HD + d] * O[m, h*HD + d]; one warp per (m, h)
-__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                                     float* __restrict__ D, int M, int H, int HD, long long o_stride, long long do_stride) {
-    const int lane = threadIdx.x & 31;
-    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (wid >= (long long)M * H) return;
-    const int h = int(wid % H);
-    const long long m = wid / H;
-    float acc = 0.f;
-    for (int d = lane * 2; d < HD; d += 64) {
-        const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + m * o_stride + h * HD + d));
-        const float2 b = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dout + m * do_stride + h * HD + d));
-        acc += a.x * b.x + a.y * b.y;
+// D[h, m] = sum_d dO[m, h*HD + d] * O[m, h*HD + d]. HD/8 consecutive lanes share one (m, h) row and
+// load 16 bytes each; every thread keeps four rows in flight.
+template <int HD>
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                                            float* __restrict__ D, long long M, int H, long long o_stride,
+                                                            long long do_stride) {
+    constexpr int LPR = HD / 8;                       // lanes per row
+    constexpr int ROWS_PER_BLOCK = 256 / LPR;
+    const int sub = threadIdx.x % LPR;
+    const long long total = M * H;
+    const long long stride = (long long)gridDim.x * ROWS_PER_BLOCK;
+    for (long long base = (long long)blockIdx.x * ROWS_PER_BLOCK + threadIdx.x / LPR; base < total; base += 4 * stride) {
+        uint4 a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long it = base + u * stride;
+            if (it < total) {
+                const long long m = it / H;
+                const int h = int(it - m * H);
+                a[u] = *reinterpret_cast<const uint4*>(o + m * o_stride + h * HD + sub * 8);
+                b[u] = *reinterpret_cast<const uint4*>(dout + m * do_stride + h * HD + sub * 8);
+            } else {
+                a[u] = make_uint4(0, 0, 0, 0);
+                b[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float2 a0 = unpack_bf16x2(a[u].x), a1 = unpack_bf16x2(a[u].y), a2 = unpack_bf16x2(a[u].z), a3 = unpack_bf16x2(a[u].w);
+            const float2 b0 = unpack_bf16x2(b[u].x), b1 = unpack_bf16x2(b[u].y), b2 = unpack_bf16x2(b[u].z), b3 = unpack_bf16x2(b[u].w);
+            float acc = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
+#pragma unroll
+            for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            const long long it = base + u * stride;
+            if (sub == 0 && it < total) {
+                const long long m = it / H;
+                const int h = int(it - m * H);
+                D[(long long)h * M + m] = acc;
+            }
+        }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) D[(long long)h * M + m] = acc;
 }
 
 // dq (fp32 accumulator, [M, H*HD]) -> inverse RoPE -> bf16 q columns of dqkv. In the same pass the
@@ -563,9 +588,16 @@ extern "C" int pb_attn_bwd(const void* qkv, const void* o, const void* dout, con
     if (rc) return rc;
     if (cudaMemsetAsync(dq_acc, 0, size_t(M) * H * HD * sizeof(float), st) != cudaSuccess) return -40;
     {
-        const long long warps = (long long)M * H;
-        attn_bwd_prep_kernel<<<unsigned((warps + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, D, M, H,
-                                                                         HD, o_stride, do_stride);
+        const long long rows = (long long)M * H;
+        const int rows_per_block = 256 / (HD / 8);
+        long long blocks = (rows + 4LL * rows_per_block - 1) / (4LL * rows_per_block);
+        if (blocks < 1) blocks = 1;
+        if (HD == 64)
+            attn_bwd_prep_kernel<64><<<unsigned(blocks), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, D, M, H,
+                                                                         o_stride, do_stride);
+        else
+            attn_bwd_prep_kernel<128><<<unsigned(blocks), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, D, M, H,
+                                                                          o_stride, do_stride);
     }
     AttnBwdParams p;
     p.M = M; p.H = H; p.KV = KV; p.n_tiles = (M + 127) / 128; p.seq_start = seq_start; p.lse2 = lse2; p.D = D;

@@ -11,11 +11,11 @@
 // Per CTA: 6 stages x (16 KB A-half + 16 KB B-half); TMEM 512 columns = two 128 x 256 fp32
 // accumulators (rows 128*rank .. of the pair's tile), so the epilogue of tile i overlaps the main
 // loop of tile i+1. Roles per CTA: warp 0 TMA producer, warp 1 TMEM owner (+ MMA issuer in the
-// leader CTA only), warps 2-5 epilogue. Cross-CTA signalling:
+// leader CTA only), warps 2-9 epilogue (two per TMEM lane quadrant, one accumulator column half each). Cross-CTA signalling:
 //   full[s]   (leader)  <- complete_tx from both CTAs' TMA loads
 //   empty[s]  (both)    <- tcgen05.commit.cta_group::2 with a 2-CTA arrive mask
 //   tfull[a]  (both)    <- same, after the last k-block of a tile
-//   tempty[a] (leader)  <- 4 local + 4 remote (mapa) arrives from the epilogue warps
+//   tempty[a] (leader)  <- 8 local + 8 remote (mapa) arrives from the epilogue warps
 // Every wait is bounded (status word + abort flag), both CTAs always reach the final cluster barrier.
 #include "gemm_common.cuh"
 #include <cooperative_groups.h>
@@ -146,8 +146,8 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 }
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
-template <bool A_MN, bool B_MN, bool GATHER>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+template <bool A_MN, bool B_MN, bool GATHER, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
                        const GatherParams g) {
     extern __shared__ uint8_t smem_raw[];
@@ -172,7 +172,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, 8);       // 4 epilogue warps x 2 CTAs
+            mbar_init(bar_tempty + 8 * a, 16);      // 8 epilogue warps x 2 CTAs
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -200,7 +200,9 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         bool ok = true;
         for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs) {
             const int m0 = (tile / p.tiles_n) * 256 + int(rank) * 128;     // my half of the A rows
-            const int n0 = (tile % p.tiles_n) * G2_BN + int(rank) * 128;   // my half of the B rows
+            // my half of the B rows; with the SwiGLU epilogue the halves are the gate rows and the matching up rows
+            const int n0 = EPI == GEMM_EPI_SWIGLU ? (tile % p.tiles_n) * 128 + int(rank) * p.epi_i0
+                                                    : (tile % p.tiles_n) * G2_BN + int(rank) * 128;
             if constexpr (GATHER) {
                 // wait until every row of this n-block has landed in the local B buffer
                 const int* ctr = g.counters + (tile % p.tiles_n);
@@ -287,11 +289,13 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
         __syncwarp();
     } else {
-        // ------------------------- epilogue (warps 2..5, both CTAs) -------------------------
+        // ------------------------- epilogue (warps 2..9, both CTAs) -------------------------
+        // warp w reads TMEM lane quadrant w & 3 (a hardware rule) and column half (w - 2) >> 2 of the accumulator
         const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row_in_half = quad * 32 + lane;
         if constexpr (GATHER) {
-            const int et = threadIdx.x - 64;                       // 0..127 within the four epilogue warps
+            const int et = threadIdx.x - 64;                       // 0..255 within the eight epilogue warps
             const int n_units = (p.N + GATHER_ROWS - 1) / GATHER_ROWS;
             const int vec_per_row = p.K / 8;                       // 16-byte vectors per row (K % 8 == 0)
             for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
@@ -301,22 +305,22 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     const __nv_bfloat16* src = g.shard[owner] + (long long)(r0 - owner * g.rows_per_rank) * g.ld;
                     __nv_bfloat16* dst = g.full + (long long)r0 * g.ld;
                     const int total = (r1 - r0) * vec_per_row;
-                    for (int i = et; i < total; i += 128 * 4) {    // 4 independent 16-byte peer loads in flight per thread
+                    for (int i = et; i < total; i += 256 * 4) {    // 4 independent 16-byte peer loads in flight per thread
                         uint4 v[4];
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const int j = i + k * 128;
+                            const int j = i + k * 256;
                             if (j < total) v[k] = *reinterpret_cast<const uint4*>(src + (long long)(j / vec_per_row) * g.ld + (j % vec_per_row) * 8);
                         }
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const int j = i + k * 128;
+                            const int j = i + k * 256;
                             if (j < total) *reinterpret_cast<uint4*>(dst + (long long)(j / vec_per_row) * g.ld + (j % vec_per_row) * 8) = v[k];
                         }
                     }
                 }
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps only
+                asm volatile("bar.sync 1, 256;" ::: "memory");      // the eight epilogue warps only
                 if (et == 0) {
                     fence_proxy_async_global();
                     asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(g.counters + r0 / G2_BN) : "memory");
@@ -336,12 +340,117 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
             tc_fence_after();
             const int row = m0 + row_in_half;
             const uint32_t t_row = tmem_base + acc * G2_BN + (uint32_t(quad * 32) << 16);
+            if constexpr (EPI == GEMM_EPI_SWIGLU) {
+                const int F = p.epi_i0;
+                const int j0 = (tile % p.tiles_n) * 128;            // feature block of this tile
 #pragma unroll 1
-            for (int c = 0; c < G2_BN; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(t_row + c, v);
-                tmem_ld_wait();
-                gemm_store_chunk(p, v, row, n0 + c);
+                for (int c = half * 64; c < half * 64 + 64; c += 32) {
+                    uint32_t vg[32], vu[32];
+                    tmem_ld32(t_row + c, vg);                       // gate: accumulator columns 0..127
+                    tmem_ld32(t_row + 128 + c, vu);                 // up:   accumulator columns 128..255
+                    tmem_ld_wait();
+                    if (row < p.M) {
+                        float g[32], u[32], a[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            g[i] = __uint_as_float(vg[i]);
+                            u[i] = __uint_as_float(vu[i]);
+                            a[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+                        }
+                        __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + j0 + c;
+                        store_bf16x32(h, g);
+                        store_bf16x32(h + F, u);
+                        store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + j0 + c, a);
+                    }
+                }
+            } else if constexpr (EPI == GEMM_EPI_DSWIGLU) {
+                const int F = p.epi_i0;
+                const int cbeg = half * 128;
+                __nv_bfloat16* hrow = reinterpret_cast<__nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + n0;
+                // gate | up of the first chunk are fetched before the accumulator is even waited for, those of
+                // chunk c + 1 while chunk c is computed: the global-load latency is paid once per tile
+                uint4 pg[4], pu[4];
+                const bool live0 = row < p.M && n0 + cbeg < p.N;
+                if (live0) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        pg[q] = *reinterpret_cast<const uint4*>(hrow + cbeg + 8 * q);
+                        pu[q] = *reinterpret_cast<const uint4*>(hrow + F + cbeg + 8 * q);
+                    }
+                }
+#pragma unroll 1
+                for (int c = cbeg; c < cbeg + 128; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(t_row + c, v);
+                    uint4 cg[4], cu[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) { cg[q] = pg[q]; cu[q] = pu[q]; }
+                    const bool live = row < p.M && n0 + c < p.N;
+                    if (c + 32 < cbeg + 128 && row < p.M && n0 + c + 32 < p.N) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            pg[q] = *reinterpret_cast<const uint4*>(hrow + c + 32 + 8 * q);
+                            pu[q] = *reinterpret_cast<const uint4*>(hrow + F + c + 32 + 8 * q);
+                        }
+                    }
+                    tmem_ld_wait();
+                    if (live) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t gw[4] = {cg[q].x, cg[q].y, cg[q].z, cg[q].w};
+                            const uint32_t uw[4] = {cu[q].x, cu[q].y, cu[q].z, cu[q].w};
+                            uint32_t og[4], ou[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                const float2 g2 = unpack_bf16x2(gw[t]), u2 = unpack_bf16x2(uw[t]);
+                                const float d0 = __uint_as_float(v[8 * q + 2 * t]), d1 = __uint_as_float(v[8 * q + 2 * t + 1]);
+                                const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+                                og[t] = pack_bf16x2(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
+                                ou[t] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
+                            }
+                            *reinterpret_cast<uint4*>(hrow + c + 8 * q) = make_uint4(og[0], og[1], og[2], og[3]);
+                            *reinterpret_cast<uint4*>(hrow + F + c + 8 * q) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+                        }
+                    }
+                }
+            } else {
+                constexpr bool rope = EPI == GEMM_EPI_ROPE;
+                const int cbeg = half * 128;
+                const float* cs_row = rope ? reinterpret_cast<const float*>(p.aux) + (long long)(row % p.epi_i0) * p.epi_i2 : nullptr;
+                float4 pc[8];     // (cos, sin) pairs of the next chunk, fetched one chunk ahead
+                if (rope && n0 + cbeg < p.epi_i1) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) pc[q] = *reinterpret_cast<const float4*>(cs_row + ((n0 + cbeg) % p.epi_i2) + 4 * q);
+                }
+#pragma unroll 1
+                for (int c = cbeg; c < cbeg + 128; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(t_row + c, v);
+                    float4 cc[8];
+                    const bool rot = rope && n0 + c < p.epi_i1;
+                    if (rot) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) cc[q] = pc[q];
+                        if (c + 32 < cbeg + 128 && n0 + c + 32 < p.epi_i1) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                pc[q] = *reinterpret_cast<const float4*>(cs_row + ((n0 + c + 32) % p.epi_i2) + 4 * q);
+                        }
+                    }
+                    tmem_ld_wait();
+                    if (rot) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {   // two (even, odd) pairs per float4: cos0 sin0 cos1 sin1
+                            const float x0 = __uint_as_float(v[4 * q]), y0 = __uint_as_float(v[4 * q + 1]);
+                            const float x1 = __uint_as_float(v[4 * q + 2]), y1 = __uint_as_float(v[4 * q + 3]);
+                            v[4 * q] = __float_as_uint(x0 * cc[q].x - y0 * cc[q].y);
+                            v[4 * q + 1] = __float_as_uint(x0 * cc[q].y + y0 * cc[q].x);
+                            v[4 * q + 2] = __float_as_uint(x1 * cc[q].z - y1 * cc[q].w);
+                            v[4 * q + 3] = __float_as_uint(x1 * cc[q].w + y1 * cc[q].z);
+                        }
+                    }
+                    gemm_store_chunk(p, v, row, n0 + c);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -358,34 +467,58 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
 }
 
-template <bool A_MN, bool B_MN, bool GATHER = false>
+template <bool A_MN, bool B_MN, bool GATHER = false, int EPI = GEMM_EPI_NONE>
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t st,
                             const GatherParams& g = GatherParams{}) {
-    auto kern = gemm_bf16_tcgen05_pair<A_MN, B_MN, GATHER>;
+    auto kern = gemm_bf16_tcgen05_pair<A_MN, B_MN, GATHER, EPI>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_BYTES) != cudaSuccess) return -20;
         configured = true;
     }
     const int tiles_m = (p.M + 255) / 256;
-    p.tiles_n = (p.N + G2_BN - 1) / G2_BN;
+    p.tiles_n = EPI == GEMM_EPI_SWIGLU ? p.epi_i0 / 128 : (p.N + G2_BN - 1) / G2_BN;
     p.num_tiles = tiles_m * p.tiles_n;
     int ctas = sm_count() & ~1;
     if (max_ctas > 0 && ctas > (max_ctas & ~1)) ctas = max_ctas & ~1;
     if (ctas > 2 * p.num_tiles) ctas = 2 * p.num_tiles;
     if (ctas < 2) ctas = 2;
-    kern<<<ctas, 192, G2_SMEM_BYTES, st>>>(tmA, tmB, p, g);
+    kern<<<ctas, 320, G2_SMEM_BYTES, st>>>(tmA, tmB, p, g);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 
 }  // namespace pb
 
+extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
+                                     long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_fp32, int max_ctas,
+                                     int epi, int epi_i0, int epi_i1, int epi_i2, void* aux, long long ldaux, int* status,
+                                     void* stream);
+
 // Same contract as pb_gemm_bf16; requires nothing more of the operands. Tile 256 x 256 per CTA pair.
 extern "C" int pb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
                                  long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_fp32, int max_ctas,
                                  int* status, void* stream) {
+    return pb_gemm_bf16_pair_epi(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, out_fp32, max_ctas, 0, 0, 0, 0, nullptr, 0,
+                                 status, stream);
+}
+
+// pb_gemm_bf16_pair with one of the fused epilogues described next to GEMM_EPI_* (bf16 output only):
+//   epi 1 (SwiGLU)  : B = [w1; w3] K-major, N = 2F, epi_i0 = F (multiple of 128), C = h13, aux = act, ldaux its pitch
+//   epi 2 (RoPE)    : epi_i0 = T, epi_i1 = number of leading columns to rotate, epi_i2 = head size, aux = fp32 table
+//   epi 3 (dSwiGLU) : N = F = epi_i0, aux = h13 (read gate | up, written d gate | d up), C unused
+extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
+                                     long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_fp32, int max_ctas,
+                                     int epi, int epi_i0, int epi_i1, int epi_i2, void* aux, long long ldaux, int* status,
+                                     void* stream) {
     using namespace pb;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (epi != GEMM_EPI_NONE) {
+        if (out_fp32 || R || !aux || (reinterpret_cast<uintptr_t>(aux) & 15)) return -4;
+        if (epi == GEMM_EPI_SWIGLU && (a_mn || b_mn || epi_i0 % 128 || N != 2 * epi_i0 || ldaux % 8)) return -4;
+        if (epi == GEMM_EPI_ROPE && (a_mn || b_mn || epi_i0 <= 0 || epi_i2 % 32 || epi_i1 % 32 || epi_i1 > N)) return -4;
+        if (epi == GEMM_EPI_DSWIGLU && (a_mn || !b_mn || N != epi_i0 || epi_i0 % 32 || ldaux % 8)) return -4;
+        if (epi < 0 || epi > GEMM_EPI_DSWIGLU) return -4;
+    }
     if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
     const int vec = out_fp32 ? 4 : 8;
     if ((ldc % vec) || (R && (ldr % vec)) || (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(R) & 15)) return -2;
@@ -399,7 +532,11 @@ extern "C" int pb_gemm_bf16_pair(const void* A, const void* B, void* C, const vo
     if (rc) return rc;
     GemmParams p{};
     p.M = M; p.N = N; p.K = K; p.C = C; p.R = R; p.ldc = ldc; p.ldr = ldr; p.out_fp32 = out_fp32; p.status = status;
+    p.epi = epi; p.epi_i0 = epi_i0; p.epi_i1 = epi_i1; p.epi_i2 = epi_i2; p.aux = aux; p.ldaux = ldaux;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (epi == GEMM_EPI_SWIGLU) return launch_gemm_pair<false, false, false, GEMM_EPI_SWIGLU>(tmA, tmB, p, max_ctas, st);
+    if (epi == GEMM_EPI_ROPE) return launch_gemm_pair<false, false, false, GEMM_EPI_ROPE>(tmA, tmB, p, max_ctas, st);
+    if (epi == GEMM_EPI_DSWIGLU) return launch_gemm_pair<false, true, false, GEMM_EPI_DSWIGLU>(tmA, tmB, p, max_ctas, st);
     if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, p, max_ctas, st);
     if (!a_mn && b_mn)  return launch_gemm_pair<false, true>(tmA, tmB, p, max_ctas, st);
     if (a_mn && !b_mn)  return launch_gemm_pair<true, false>(tmA, tmB, p, max_ctas, st);

@@ -17,8 +17,32 @@ struct GemmParams {
     int out_fp32;
     int* status;
     int num_tiles, tiles_n;
+    // fused epilogues of the CTA-pair kernel (GEMM_EPI_*); 0 = plain store
+    int epi, epi_i0, epi_i1, epi_i2;
+    void* aux;
+    long long ldaux;
 };
 
+// Epilogues fused into the CTA-pair GEMM:
+//  SWIGLU : B = [w1; w3] ([2F, K], F = epi_i0). A tile is 128 gate columns AND the matching 128 up
+//           columns (the two CTAs of the pair load those two row ranges of B), so one thread holds
+//           gate and up of the same feature: it stores both into C = h13 [M, 2F] and
+//           silu(gate) * up into aux = act [M, F].
+//  ROPE   : rotary embedding of the leading epi_i1 output columns (heads of epi_i2 columns,
+//           position = row % epi_i0, aux = fp32 table [T, hd/2, 2] of (cos, sin)) before the store.
+//  DSWIGLU: the product is d(act) [M, F = epi_i0]; aux = h13 [M, 2F] holds gate | up and is overwritten
+//           in place with d(gate) | d(up). Nothing is written to C.
+constexpr int GEMM_EPI_NONE = 0, GEMM_EPI_SWIGLU = 1, GEMM_EPI_ROPE = 2, GEMM_EPI_DSWIGLU = 3;
+
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&f)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        uint4 o;
+        o.x = pack_bf16x2(f[j], f[j + 1]); o.y = pack_bf16x2(f[j + 2], f[j + 3]);
+        o.z = pack_bf16x2(f[j + 4], f[j + 5]); o.w = pack_bf16x2(f[j + 6], f[j + 7]);
+        *reinterpret_cast<uint4*>(dst + j) = o;
+    }
+}
 // v: 32 consecutive fp32 accumulator columns of output row `row`, starting at column `col`.
 __device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, const uint32_t (&v)[32], int row, int col) {
     if (row >= p.M || col >= p.N) return;

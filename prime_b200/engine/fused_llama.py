@@ -86,7 +86,7 @@ class FusedLlama:
 
     def __init__(self, args: ModelArgs, device: torch.device | str = "cuda", comm=None, grad_dtype=torch.bfloat16,
                  ac_ckpt: bool | int = False, ce_chunk_tokens: int = 8192, z_mode: int = K.Z_NONE, z_weight: float = 0.0,
-                 comm_ctas: int = 32):
+                 comm_ctas: int = 148):
         self.args = args
         self.device = torch.device(device)
         self.comm = comm if comm is not None else LocalComm()
@@ -231,8 +231,7 @@ class FusedLlama:
         rstd1 = self._saved(i, "rstd1", (M,), torch.float32)
         K.rmsnorm_fwd(x, self.w[pre + "attention_norm.weight"], a.norm_eps, out=xn, rstd=rstd1)
         qkv = self._saved(i, "qkv", (M, (H + 2 * KV) * hd))
-        K.gemm(xn, self.wqkv[i], out=qkv)
-        K.rope_(qkv, self._rope, T, H + KV, hd)
+        K.gemm_rope(xn, self.wqkv[i], qkv, self._rope, T, H + KV, hd)     # rotary embedding in the GEMM epilogue
         o = self._saved(i, "o", (M, H * hd))
         _, lse2 = A.attention_fwd(qkv, seq_start, H, KV, hd, out=o)
         self._ws[f"L{i}.lse2" if not self._is_ckpt(i) else "Lshared.lse2"] = lse2
@@ -242,9 +241,8 @@ class FusedLlama:
         rstd2 = self._saved(i, "rstd2", (M,), torch.float32)
         K.rmsnorm_fwd(h, self.w[pre + "ffn_norm.weight"], a.norm_eps, out=hn, rstd=rstd2)
         h13 = self._saved(i, "h13", (M, 2 * F))
-        K.gemm(hn, self.w13[i], out=h13)
         act = self._saved(i, "act", (M, F))
-        K.swiglu_fwd(h13, out=act)
+        K.gemm_swiglu(hn, self.w13[i], h13, act)                          # SwiGLU in the GEMM epilogue
         K.gemm(act, self.w[pre + "feed_forward.w2.weight"], out=out, residual=h)
 
     def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, g: torch.Tensor) -> None:
@@ -264,10 +262,10 @@ class FusedLlama:
         h, hn, rstd2 = sv("h", (M, D)), sv("hn", (M, D)), sv("rstd2", (M,), torch.float32)
         h13, act = sv("h13", (M, 2 * F)), sv("act", (M, F))
         # out = h + act @ w2^T
-        dact = self._buf("dact", (M, F))
-        K.gemm(dout, self.w[pre + "feed_forward.w2.weight"], out=dact, b_mn=True)
         self._wgrad(dout, act, self.g[pre + "feed_forward.w2.weight"])
-        K.swiglu_bwd(h13, dact, dh13=h13)                       # in place: h13 becomes d(h13)
+        # in place: h13 becomes d(h13); d(act) = dout @ w2 stays inside the GEMM whose epilogue does the SwiGLU backward
+        K.gemm_dswiglu(dout, self.w[pre + "feed_forward.w2.weight"], h13,
+                       dact_ws=None if dout.is_cuda else self._buf("dact", (M, F)))
         dhn = self._buf("dhn", (M, D))
         K.gemm(h13, self.w13[i], out=dhn, b_mn=True)
         self._wgrad(h13, hn, self.g13[i])

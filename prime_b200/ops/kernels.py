@@ -92,6 +92,62 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, resi
     return out
 
 
+def _pair_ok(M: int, N: int) -> bool:
+    return _GEMM_PAIR and M >= 512 and N >= 256
+
+
+def _gemm_epi(a, b, out, M, N, K, b_mn, epi, i0, i1, i2, aux, what):
+    rc = native.cuda().pb_gemm_bf16_pair_epi(ptr(a), ptr(b), ptr(out), None, M, N, K, a.stride(0), b.stride(0),
+                                             out.stride(0) if out is not None else 0, 0, 0, int(b_mn), 0, 0, epi, i0, i1, i2,
+                                             ptr(aux), aux.stride(0) if aux.dim() == 2 else 0, ptr(status_word(a.device)),
+                                             stream_ptr())
+    check(rc, f"pb_gemm_bf16_pair_epi[{what}](M={M},N={N},K={K})")
+
+
+def gemm_swiglu(x: torch.Tensor, w13: torch.Tensor, h13: torch.Tensor, act: torch.Tensor):
+    """``h13 = x @ w13.T`` (``w13 = [w1; w3]``, ``[2F, K]``) and ``act = silu(h13[:, :F]) * h13[:, F:]`` in one
+    kernel: the SwiGLU runs in the GEMM epilogue on the fp32 accumulators (csrc/gemm2_sm100.cu). Falls
+    back to GEMM + swiglu_fwd where the fused kernel does not apply (CPU, small or odd shapes)."""
+    M, K = x.shape
+    F = w13.shape[0] // 2
+    if x.is_cuda and _pair_ok(M, 2 * F) and F % 128 == 0 and h13.stride(-1) == 1 and act.stride(-1) == 1:
+        _gemm_epi(x, w13, h13, M, 2 * F, K, False, 1, F, 0, 0, act, "swiglu")
+        return h13, act
+    gemm(x, w13, out=h13)
+    swiglu_fwd(h13, out=act)
+    return h13, act
+
+
+def gemm_dswiglu(dout: torch.Tensor, w2: torch.Tensor, h13: torch.Tensor, dact_ws: torch.Tensor | None = None):
+    """In place ``h13 <- d(h13)`` for ``out = act @ w2.T``: ``d(act) = dout @ w2`` never leaves the GEMM, its
+    epilogue reads gate | up from ``h13`` and writes d gate | d up back. ``w2`` is ``[D, F]``. Falls back to
+    GEMM (into ``dact_ws``) + swiglu_bwd where the fused kernel does not apply."""
+    M = dout.shape[0]
+    F = w2.shape[1]
+    if dout.is_cuda and _pair_ok(M, F) and F % 32 == 0 and h13.stride(-1) == 1:
+        _gemm_epi(dout, w2, None, M, F, dout.shape[1], True, 3, F, 0, 0, h13, "dswiglu")
+        return h13
+    if dact_ws is None:
+        dact_ws = torch.empty(M, F, dtype=h13.dtype, device=h13.device)
+    gemm(dout, w2, out=dact_ws, b_mn=True)
+    swiglu_bwd(h13, dact_ws, dh13=h13)
+    return h13
+
+
+def gemm_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, table: torch.Tensor, seq_len: int, n_rot_heads: int,
+              head_dim: int):
+    """``out = x @ w.T`` with the rotary embedding applied to the leading ``n_rot_heads`` heads of every output
+    row (position = row index modulo ``seq_len``) before the store. Falls back to GEMM + rope_."""
+    M, K = x.shape
+    N = w.shape[0]
+    if x.is_cuda and _pair_ok(M, N) and head_dim % 32 == 0 and out.stride(-1) == 1 and table.shape[0] >= seq_len:
+        _gemm_epi(x, w, out, M, N, K, False, 2, seq_len, n_rot_heads * head_dim, head_dim, table, "rope")
+        return out
+    gemm(x, w, out=out)
+    rope_(out, table, seq_len, n_rot_heads, head_dim)
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 # RMSNorm
 # ---------------------------------------------------------------------------------------------

@@ -38,6 +38,55 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn, bn):
     ops.check_status()
 
 
+@pytest.mark.parametrize("M,F,K", [(1024, 256, 192), (2000, 1024, 512), (4096, 4096, 1024)])
+def test_gemm_fused_swiglu_epilogues(M, F, K):
+    """SwiGLU forward and backward fused into the CTA-pair GEMM epilogue vs plain fp32 math."""
+    torch.manual_seed(0)
+    dev = "cuda"
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w13 = (torch.randn(2 * F, K, device=dev) * K ** -0.5).bfloat16()
+    h13 = torch.empty(M, 2 * F, device=dev, dtype=torch.bfloat16)
+    act = torch.empty(M, F, device=dev, dtype=torch.bfloat16)
+    ops.gemm_swiglu(x, w13, h13, act)
+    ref = x.float() @ w13.float().t()
+    g, u = ref[:, :F], ref[:, F:]
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel(h13, ref) < 1e-2
+    assert _rel(act, torch.nn.functional.silu(g) * u) < 1e-2
+    # backward: out = act @ w2.T, d(h13) from dout
+    D = 256
+    w2 = (torch.randn(D, F, device=dev) * F ** -0.5).bfloat16()
+    dout = torch.randn(M, D, device=dev, dtype=torch.bfloat16)
+    gb, ub = h13[:, :F].float(), h13[:, F:].float()
+    dact = dout.float() @ w2.float()
+    sg = torch.sigmoid(gb)
+    ref_d = torch.cat([dact * ub * sg * (1 + gb * (1 - sg)), dact * gb * sg], 1)
+    ops.gemm_dswiglu(dout, w2, h13)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel(h13, ref_d) < 1.5e-2
+
+
+@pytest.mark.parametrize("M,H,KV,hd,K,T", [(1024, 4, 4, 64, 256, 256), (3000, 8, 2, 128, 512, 1000), (4096, 16, 16, 64, 1024, 1024)])
+def test_gemm_fused_rope_epilogue(M, H, KV, hd, K, T):
+    torch.manual_seed(0)
+    dev = "cuda"
+    N = (H + 2 * KV) * hd
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=dev) * K ** -0.5).bfloat16()
+    table = ops.rope_table(T, hd, 10000.0, dev)
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    ops.gemm_rope(x, w, out, table, T, H + KV, hd)
+    ref = (x.float() @ w.float().t())
+    ref = ops.rope_(ref.cpu(), table.cpu(), T, H + KV, hd).to(dev)      # CPU twin rotates fp32 in place
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel(out, ref) < 1e-2
+    # the rotated part really differs from the unrotated product
+    assert _rel(out[:, : (H + KV) * hd], (x.float() @ w.float().t())[:, : (H + KV) * hd]) > 0.1
+
+
 def test_gemm_persistent_many_tiles():
     torch.manual_seed(1)
     a = torch.randn(8192, 1024, device="cuda", dtype=torch.bfloat16)
