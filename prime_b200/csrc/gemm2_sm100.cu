@@ -22,11 +22,19 @@
 
 namespace pb {
 
-constexpr int G2_STAGES = 6;
+constexpr int G2_STAGES = 5;
 constexpr int G2_HALF_BYTES = 128 * BK * 2;               // 16 KB: 128 rows x 64 bf16
 constexpr int G2_STAGE_BYTES = 2 * G2_HALF_BYTES;         // per CTA
 constexpr int G2_BN = 256;
-constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 + 256;
+constexpr int G2_BOX_BYTES = 128 * 64 * 2;                // one epilogue staging box: 128 rows x 64 bf16, 128B-swizzled
+constexpr int G2_EPI_BOXES = 4;
+constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + G2_EPI_BOXES * G2_BOX_BYTES + 1024 + 256;
+
+// output-side tensor maps of the staged epilogue (bf16, box = 64 columns x 128 rows)
+struct EpiMaps {
+    CUtensorMap c;      // C
+    CUtensorMap aux;    // SwiGLU: act; dSwiGLU: h13
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -148,17 +156,20 @@ __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence
 
 template <bool A_MN, bool B_MN, bool GATHER, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
-gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
-                       const GatherParams g) {
+gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ EpiMaps em, const GemmParams p, const GatherParams g) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + G2_STAGES * G2_STAGE_BYTES);
+    const uint32_t s_epi = smem_base + G2_STAGES * G2_STAGE_BYTES;      // [G2_EPI_BOXES] staging boxes
+    uint8_t* g_epi = smem_gen + G2_STAGES * G2_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + G2_STAGES * G2_STAGE_BYTES + G2_EPI_BOXES * G2_BOX_BYTES);
     const uint32_t bar_full = smem_u32(bars);                     // [STAGES]   used in the leader
     const uint32_t bar_empty = bar_full + 8 * G2_STAGES;          // [STAGES]   each CTA
     const uint32_t bar_tfull = bar_empty + 8 * G2_STAGES;         // [2]        each CTA
     const uint32_t bar_tempty = bar_tfull + 16;                   // [2]        used in the leader
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * G2_STAGES + 4);
+    const uint32_t bar_eload = bar_tempty + 16;                   // [2]        staged epilogue: input boxes have landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * G2_STAGES + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -173,6 +184,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull + 8 * a, 1);
             mbar_init(bar_tempty + 8 * a, 16);      // 8 epilogue warps x 2 CTAs
+            mbar_init(bar_eload + 8 * a, 1);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -327,8 +339,27 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 }
             }
         }
+        // The bf16 epilogues go through shared memory: every thread writes its row piece of a
+        // 128-row x 64-column box (128B-swizzled), one thread hands the box to TMA. Global memory then sees
+        // whole 128-byte rows instead of 64-byte pieces 32 rows apart; the fused SwiGLU backward also
+        // fetches its inputs that way, one block ahead. fp32 outputs and residual adds use direct stores.
+        const int et = threadIdx.x - 64;                           // 0..255 within the eight epilogue warps
+        const bool staged = EPI == GEMM_EPI_SWIGLU || EPI == GEMM_EPI_DSWIGLU || p.staged;
+        auto epi_sync = [] { asm volatile("bar.sync 2, 256;" ::: "memory"); };
+        // this thread's 64-byte piece (32 bf16 = chunks ch0..ch0+3 of 16 bytes) of row r in a staging box
+        auto box_off = [&](int box, int ch) { return box * G2_BOX_BYTES + row_in_half * 128 + (((ch) ^ (row_in_half & 7)) << 4); };
         int local = 0;
+        uint32_t rounds = 0;                                       // staged rounds done (buffer / phase bookkeeping)
         bool ok = true;
+        if constexpr (EPI == GEMM_EPI_DSWIGLU) {
+            // gate | up of the first block of the first tile
+            if (et == 0 && pair < p.num_tiles) {
+                const int m0 = (pair / p.tiles_n) * 256 + int(rank) * 128, n0 = (pair % p.tiles_n) * G2_BN;
+                mbar_expect_tx(bar_eload, 2 * G2_BOX_BYTES);
+                tma_load_2d(s_epi, &em.aux, bar_eload, n0, m0);
+                tma_load_2d(s_epi + G2_BOX_BYTES, &em.aux, bar_eload, p.epi_i0 + n0, m0);
+            }
+        }
         for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs, ++local) {
             const int acc = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
@@ -340,65 +371,86 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
             tc_fence_after();
             const int row = m0 + row_in_half;
             const uint32_t t_row = tmem_base + acc * G2_BN + (uint32_t(quad * 32) << 16);
+            auto release_acc = [&] {   // this warp has read all it needs of the accumulator
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(lead_tempty + 8 * acc);
+            };
             if constexpr (EPI == GEMM_EPI_SWIGLU) {
+                // two rounds of 64 features: boxes 0, 1, 2 = gate, up, act; this warp does 32 of the 64 columns
                 const int F = p.epi_i0;
-                const int j0 = (tile % p.tiles_n) * 128;            // feature block of this tile
+                const int j0 = (tile % p.tiles_n) * 128;
 #pragma unroll 1
-                for (int c = half * 64; c < half * 64 + 64; c += 32) {
+                for (int rnd = 0; rnd < 2; ++rnd) {
                     uint32_t vg[32], vu[32];
-                    tmem_ld32(t_row + c, vg);                       // gate: accumulator columns 0..127
-                    tmem_ld32(t_row + 128 + c, vu);                 // up:   accumulator columns 128..255
+                    tmem_ld32(t_row + rnd * 64 + half * 32, vg);          // gate: accumulator columns 0..127
+                    tmem_ld32(t_row + 128 + rnd * 64 + half * 32, vu);    // up:   accumulator columns 128..255
+                    if (et == 0) tma_store_wait_read<0>();                // the boxes of the previous round have been read
+                    epi_sync();
                     tmem_ld_wait();
-                    if (row < p.M) {
-                        float g[32], u[32], a[32];
+                    if (rnd == 1) release_acc();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            g[i] = __uint_as_float(vg[i]);
-                            u[i] = __uint_as_float(vu[i]);
-                            a[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t og[4], ou[4], oa[4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const float g0 = __uint_as_float(vg[8 * q + 2 * t]), g1 = __uint_as_float(vg[8 * q + 2 * t + 1]);
+                            const float u0 = __uint_as_float(vu[8 * q + 2 * t]), u1 = __uint_as_float(vu[8 * q + 2 * t + 1]);
+                            og[t] = pack_bf16x2(g0, g1);
+                            ou[t] = pack_bf16x2(u0, u1);
+                            oa[t] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
                         }
-                        __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + j0 + c;
-                        store_bf16x32(h, g);
-                        store_bf16x32(h + F, u);
-                        store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + j0 + c, a);
+                        *reinterpret_cast<uint4*>(g_epi + box_off(0, half * 4 + q)) = make_uint4(og[0], og[1], og[2], og[3]);
+                        *reinterpret_cast<uint4*>(g_epi + box_off(1, half * 4 + q)) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+                        *reinterpret_cast<uint4*>(g_epi + box_off(2, half * 4 + q)) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+                    }
+                    fence_proxy_async_smem();
+                    epi_sync();
+                    if (et == 0) {
+                        tma_store_2d(&em.c, s_epi, j0 + rnd * 64, m0);
+                        tma_store_2d(&em.c, s_epi + G2_BOX_BYTES, F + j0 + rnd * 64, m0);
+                        tma_store_2d(&em.aux, s_epi + 2 * G2_BOX_BYTES, j0 + rnd * 64, m0);
+                        tma_store_commit();
                     }
                 }
             } else if constexpr (EPI == GEMM_EPI_DSWIGLU) {
+                // four rounds of 64 columns of d(act); buffer b = boxes 2b (gate) and 2b+1 (up), rewritten in place
                 const int F = p.epi_i0;
-                const int cbeg = half * 128;
-                __nv_bfloat16* hrow = reinterpret_cast<__nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + n0;
-                // gate | up of the first chunk are fetched before the accumulator is even waited for, those of
-                // chunk c + 1 while chunk c is computed: the global-load latency is paid once per tile
-                uint4 pg[4], pu[4];
-                const bool live0 = row < p.M && n0 + cbeg < p.N;
-                if (live0) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        pg[q] = *reinterpret_cast<const uint4*>(hrow + cbeg + 8 * q);
-                        pu[q] = *reinterpret_cast<const uint4*>(hrow + F + cbeg + 8 * q);
-                    }
-                }
 #pragma unroll 1
-                for (int c = cbeg; c < cbeg + 128; c += 32) {
+                for (int rnd = 0; rnd < 4; ++rnd, ++rounds) {
+                    const int buf = rounds & 1;
                     uint32_t v[32];
-                    tmem_ld32(t_row + c, v);
-                    uint4 cg[4], cu[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) { cg[q] = pg[q]; cu[q] = pu[q]; }
-                    const bool live = row < p.M && n0 + c < p.N;
-                    if (c + 32 < cbeg + 128 && row < p.M && n0 + c + 32 < p.N) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            pg[q] = *reinterpret_cast<const uint4*>(hrow + c + 32 + 8 * q);
-                            pu[q] = *reinterpret_cast<const uint4*>(hrow + F + c + 32 + 8 * q);
+                    tmem_ld32(t_row + rnd * 64 + half * 32, v);
+                    if (et == 0) {
+                        // fetch the next block (of this tile or of the next one) into the other buffer
+                        int nt = tile, nr = rnd + 1;
+                        if (nr == 4) { nr = 0; nt += n_pairs; }
+                        if (nt < p.num_tiles) {
+                            const int nm0 = (nt / p.tiles_n) * 256 + int(rank) * 128, nn0 = (nt % p.tiles_n) * G2_BN + nr * 64;
+                            tma_store_wait_read<0>();      // the stores that last used that buffer have read it
+                            if (nn0 < p.N) {
+                                mbar_expect_tx(bar_eload + 8 * (buf ^ 1), 2 * G2_BOX_BYTES);
+                                tma_load_2d(s_epi + (2 * (buf ^ 1)) * G2_BOX_BYTES, &em.aux, bar_eload + 8 * (buf ^ 1), nn0, nm0);
+                                tma_load_2d(s_epi + (2 * (buf ^ 1) + 1) * G2_BOX_BYTES, &em.aux, bar_eload + 8 * (buf ^ 1), F + nn0, nm0);
+                            } else {
+                                mbar_arrive(bar_eload + 8 * (buf ^ 1));   // block past N: nothing to fetch, keep the phases in step
+                            }
                         }
                     }
+                    ok = mbar_wait(bar_eload + 8 * buf, (rounds >> 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
+                    ok = __all_sync(0xffffffffu, ok);
                     tmem_ld_wait();
+                    if (rnd == 3) release_acc();
+                    if (!ok) break;
+                    const bool live = n0 + rnd * 64 < p.N;
                     if (live) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            const uint32_t gw[4] = {cg[q].x, cg[q].y, cg[q].z, cg[q].w};
-                            const uint32_t uw[4] = {cu[q].x, cu[q].y, cu[q].z, cu[q].w};
+                            uint4* pg = reinterpret_cast<uint4*>(g_epi + box_off(2 * buf, half * 4 + q));
+                            uint4* pu = reinterpret_cast<uint4*>(g_epi + box_off(2 * buf + 1, half * 4 + q));
+                            const uint4 cg = *pg, cu = *pu;
+                            const uint32_t gw[4] = {cg.x, cg.y, cg.z, cg.w};
+                            const uint32_t uw[4] = {cu.x, cu.y, cu.z, cu.w};
                             uint32_t og[4], ou[4];
 #pragma unroll
                             for (int t = 0; t < 4; ++t) {
@@ -408,54 +460,83 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                                 og[t] = pack_bf16x2(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
                                 ou[t] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
                             }
-                            *reinterpret_cast<uint4*>(hrow + c + 8 * q) = make_uint4(og[0], og[1], og[2], og[3]);
-                            *reinterpret_cast<uint4*>(hrow + F + c + 8 * q) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+                            *pg = make_uint4(og[0], og[1], og[2], og[3]);
+                            *pu = make_uint4(ou[0], ou[1], ou[2], ou[3]);
                         }
+                    }
+                    fence_proxy_async_smem();
+                    epi_sync();
+                    if (et == 0 && live) {
+                        tma_store_2d(&em.aux, s_epi + (2 * buf) * G2_BOX_BYTES, n0 + rnd * 64, m0);
+                        tma_store_2d(&em.aux, s_epi + (2 * buf + 1) * G2_BOX_BYTES, F + n0 + rnd * 64, m0);
+                        tma_store_commit();
+                    }
+                }
+            } else if (staged) {
+                // two rounds of 128 columns; buffer b = boxes 2b, 2b+1; this warp fills box `half` of the round
+                constexpr bool rope = EPI == GEMM_EPI_ROPE;
+                const float* cs_row = rope ? reinterpret_cast<const float*>(p.aux) + (long long)(row % p.epi_i0) * p.epi_i2 : nullptr;
+#pragma unroll 1
+                for (int rnd = 0; rnd < 2; ++rnd, ++rounds) {
+                    const int buf = rounds & 1;
+                    const int cb = n0 + rnd * 128 + half * 64;             // first column of this warp's box
+                    uint32_t v0[32], v1[32];
+                    tmem_ld32(t_row + rnd * 128 + half * 64, v0);
+                    tmem_ld32(t_row + rnd * 128 + half * 64 + 32, v1);
+                    float4 cs[16];
+                    const bool rot = rope && cb < p.epi_i1;
+                    if (rot) {
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) cs[q] = *reinterpret_cast<const float4*>(cs_row + (cb % p.epi_i2) + 4 * q);
+                    }
+                    if (et == 0) tma_store_wait_read<1>();                 // the stores that last used this buffer have read it
+                    epi_sync();
+                    tmem_ld_wait();
+                    if (rnd == 1) release_acc();
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        uint32_t (&v)[32] = hh ? v1 : v0;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                float x = __uint_as_float(v[8 * q + 2 * t]), y = __uint_as_float(v[8 * q + 2 * t + 1]);
+                                if (rot) {   // (even, odd) pair idx within the 64-column box: hh*16 + 4q + t
+                                    const float4 c4 = cs[(hh * 16 + 4 * q + t) >> 1];
+                                    const float co = (t & 1) ? c4.z : c4.x, si = (t & 1) ? c4.w : c4.y;
+                                    const float xr = x * co - y * si;
+                                    y = x * si + y * co;
+                                    x = xr;
+                                }
+                                o[t] = pack_bf16x2(x, y);
+                            }
+                            *reinterpret_cast<uint4*>(g_epi + box_off(2 * buf + half, hh * 4 + q)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    epi_sync();
+                    if (et == 0) {
+#pragma unroll
+                        for (int h2 = 0; h2 < 2; ++h2)
+                            if (n0 + rnd * 128 + h2 * 64 < p.N)
+                                tma_store_2d(&em.c, s_epi + (2 * buf + h2) * G2_BOX_BYTES, n0 + rnd * 128 + h2 * 64, m0);
+                        tma_store_commit();
                     }
                 }
             } else {
-                constexpr bool rope = EPI == GEMM_EPI_ROPE;
                 const int cbeg = half * 128;
-                const float* cs_row = rope ? reinterpret_cast<const float*>(p.aux) + (long long)(row % p.epi_i0) * p.epi_i2 : nullptr;
-                float4 pc[8];     // (cos, sin) pairs of the next chunk, fetched one chunk ahead
-                if (rope && n0 + cbeg < p.epi_i1) {
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) pc[q] = *reinterpret_cast<const float4*>(cs_row + ((n0 + cbeg) % p.epi_i2) + 4 * q);
-                }
 #pragma unroll 1
                 for (int c = cbeg; c < cbeg + 128; c += 32) {
                     uint32_t v[32];
                     tmem_ld32(t_row + c, v);
-                    float4 cc[8];
-                    const bool rot = rope && n0 + c < p.epi_i1;
-                    if (rot) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) cc[q] = pc[q];
-                        if (c + 32 < cbeg + 128 && n0 + c + 32 < p.epi_i1) {
-#pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                pc[q] = *reinterpret_cast<const float4*>(cs_row + ((n0 + c + 32) % p.epi_i2) + 4 * q);
-                        }
-                    }
                     tmem_ld_wait();
-                    if (rot) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {   // two (even, odd) pairs per float4: cos0 sin0 cos1 sin1
-                            const float x0 = __uint_as_float(v[4 * q]), y0 = __uint_as_float(v[4 * q + 1]);
-                            const float x1 = __uint_as_float(v[4 * q + 2]), y1 = __uint_as_float(v[4 * q + 3]);
-                            v[4 * q] = __float_as_uint(x0 * cc[q].x - y0 * cc[q].y);
-                            v[4 * q + 1] = __float_as_uint(x0 * cc[q].y + y0 * cc[q].x);
-                            v[4 * q + 2] = __float_as_uint(x1 * cc[q].z - y1 * cc[q].w);
-                            v[4 * q + 3] = __float_as_uint(x1 * cc[q].w + y1 * cc[q].z);
-                        }
-                    }
                     gemm_store_chunk(p, v, row, n0 + c);
                 }
+                release_acc();
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(lead_tempty + 8 * acc);
         }
+        if (et == 0) tma_store_wait<0>();   // every staged store of this CTA has landed
     }
 
     tc_fence_before();
@@ -469,7 +550,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
 template <bool A_MN, bool B_MN, bool GATHER = false, int EPI = GEMM_EPI_NONE>
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t st,
-                            const GatherParams& g = GatherParams{}) {
+                            const GatherParams& g = GatherParams{}, const EpiMaps& em = EpiMaps{}) {
     auto kern = gemm_bf16_tcgen05_pair<A_MN, B_MN, GATHER, EPI>;
     static bool configured = false;
     if (!configured) {
@@ -483,7 +564,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
     if (max_ctas > 0 && ctas > (max_ctas & ~1)) ctas = max_ctas & ~1;
     if (ctas > 2 * p.num_tiles) ctas = 2 * p.num_tiles;
     if (ctas < 2) ctas = 2;
-    kern<<<ctas, 320, G2_SMEM_BYTES, st>>>(tmA, tmB, p, g);
+    kern<<<ctas, 320, G2_SMEM_BYTES, st>>>(tmA, tmB, em, p, g);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 
@@ -515,8 +596,8 @@ extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, cons
     if (epi != GEMM_EPI_NONE) {
         if (out_fp32 || R || !aux || (reinterpret_cast<uintptr_t>(aux) & 15)) return -4;
         if (epi == GEMM_EPI_SWIGLU && (a_mn || b_mn || epi_i0 % 128 || N != 2 * epi_i0 || ldaux % 8)) return -4;
-        if (epi == GEMM_EPI_ROPE && (a_mn || b_mn || epi_i0 <= 0 || epi_i2 % 32 || epi_i1 % 32 || epi_i1 > N)) return -4;
-        if (epi == GEMM_EPI_DSWIGLU && (a_mn || !b_mn || N != epi_i0 || epi_i0 % 32 || ldaux % 8)) return -4;
+        if (epi == GEMM_EPI_ROPE && (a_mn || b_mn || epi_i0 <= 0 || epi_i2 % 64 || epi_i1 % 64 || epi_i1 > N)) return -4;
+        if (epi == GEMM_EPI_DSWIGLU && (a_mn || !b_mn || N != epi_i0 || epi_i0 % 64 || ldaux % 8)) return -4;
         if (epi < 0 || epi > GEMM_EPI_DSWIGLU) return -4;
     }
     if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
@@ -533,14 +614,25 @@ extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, cons
     GemmParams p{};
     p.M = M; p.N = N; p.K = K; p.C = C; p.R = R; p.ldc = ldc; p.ldr = ldr; p.out_fp32 = out_fp32; p.status = status;
     p.epi = epi; p.epi_i0 = epi_i0; p.epi_i1 = epi_i1; p.epi_i2 = epi_i2; p.aux = aux; p.ldaux = ldaux;
+    // bf16 tiles without a residual leave through shared memory + TMA stores
+    p.staged = (!out_fp32 && !R && epi != GEMM_EPI_DSWIGLU) ? 1 : 0;
+    EpiMaps em{};
+    if (p.staged) {
+        rc = make_tmap_bf16_2d(&em.c, C, N, M, ldc, 64, 128);
+        if (rc) return rc;
+    }
+    if (epi == GEMM_EPI_SWIGLU) rc = make_tmap_bf16_2d(&em.aux, aux, epi_i0, M, ldaux, 64, 128);
+    if (epi == GEMM_EPI_DSWIGLU) rc = make_tmap_bf16_2d(&em.aux, aux, 2 * uint64_t(epi_i0), M, ldaux, 64, 128);
+    if (rc) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (epi == GEMM_EPI_SWIGLU) return launch_gemm_pair<false, false, false, GEMM_EPI_SWIGLU>(tmA, tmB, p, max_ctas, st);
-    if (epi == GEMM_EPI_ROPE) return launch_gemm_pair<false, false, false, GEMM_EPI_ROPE>(tmA, tmB, p, max_ctas, st);
-    if (epi == GEMM_EPI_DSWIGLU) return launch_gemm_pair<false, true, false, GEMM_EPI_DSWIGLU>(tmA, tmB, p, max_ctas, st);
-    if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, p, max_ctas, st);
-    if (!a_mn && b_mn)  return launch_gemm_pair<false, true>(tmA, tmB, p, max_ctas, st);
-    if (a_mn && !b_mn)  return launch_gemm_pair<true, false>(tmA, tmB, p, max_ctas, st);
-    return launch_gemm_pair<true, true>(tmA, tmB, p, max_ctas, st);
+    const GatherParams ng{};
+    if (epi == GEMM_EPI_SWIGLU) return launch_gemm_pair<false, false, false, GEMM_EPI_SWIGLU>(tmA, tmB, p, max_ctas, st, ng, em);
+    if (epi == GEMM_EPI_ROPE) return launch_gemm_pair<false, false, false, GEMM_EPI_ROPE>(tmA, tmB, p, max_ctas, st, ng, em);
+    if (epi == GEMM_EPI_DSWIGLU) return launch_gemm_pair<false, true, false, GEMM_EPI_DSWIGLU>(tmA, tmB, p, max_ctas, st, ng, em);
+    if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, p, max_ctas, st, ng, em);
+    if (!a_mn && b_mn)  return launch_gemm_pair<false, true>(tmA, tmB, p, max_ctas, st, ng, em);
+    if (a_mn && !b_mn)  return launch_gemm_pair<true, false>(tmA, tmB, p, max_ctas, st, ng, em);
+    return launch_gemm_pair<true, true>(tmA, tmB, p, max_ctas, st, ng, em);
 }
 
 // All-gather fused GEMM: C[M,N] = A[M,K] * B[N,K]^T (+R) where B is row-sharded over `world` ranks.

@@ -19,6 +19,7 @@ struct GemmParams {
     int num_tiles, tiles_n;
     // fused epilogues of the CTA-pair kernel (GEMM_EPI_*); 0 = plain store
     int epi, epi_i0, epi_i1, epi_i2;
+    int staged;      // plain / RoPE epilogue: 1 = stage the bf16 tile in shared memory and store it with TMA
     void* aux;
     long long ldaux;
 };

@@ -124,7 +124,7 @@ def gemm_dswiglu(dout: torch.Tensor, w2: torch.Tensor, h13: torch.Tensor, dact_w
     GEMM (into ``dact_ws``) + swiglu_bwd where the fused kernel does not apply."""
     M = dout.shape[0]
     F = w2.shape[1]
-    if dout.is_cuda and _pair_ok(M, F) and F % 32 == 0 and h13.stride(-1) == 1:
+    if dout.is_cuda and _pair_ok(M, F) and F % 64 == 0 and h13.stride(-1) == 1:
         _gemm_epi(dout, w2, None, M, F, dout.shape[1], True, 3, F, 0, 0, h13, "dswiglu")
         return h13
     if dact_ws is None:
@@ -140,7 +140,7 @@ def gemm_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, table: torch.
     row (position = row index modulo ``seq_len``) before the store. Falls back to GEMM + rope_."""
     M, K = x.shape
     N = w.shape[0]
-    if x.is_cuda and _pair_ok(M, N) and head_dim % 32 == 0 and out.stride(-1) == 1 and table.shape[0] >= seq_len:
+    if x.is_cuda and _pair_ok(M, N) and head_dim % 64 == 0 and out.stride(-1) == 1 and table.shape[0] >= seq_len:
         _gemm_epi(x, w, out, M, N, K, False, 2, seq_len, n_rot_heads * head_dim, head_dim, table, "rope")
         return out
     gemm(x, w, out=out)
