@@ -511,3 +511,47 @@ extern "C" int pb_add_bf16(const void* a, const void* b, void* out, long long n,
     add_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, n / 8);
     return CHECK_LAUNCH();
 }
+
+// out[r, c] = sum_s ws[s][r][c] (+ res[r, c]); ws is fp32 [slices][M][N] (N % 4 == 0), out / res are bf16 or fp32
+template <bool OUT_FP32>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, int slices, long long M, int N, const void* res,
+                                                            long long ld_res, void* out, long long ld_out) {
+    const int vpr = N / 4;
+    const long long total = M * vpr;
+    const long long slice_stride = M * (long long)N;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / vpr;
+        const int c = int(i % vpr) * 4;
+        float4 acc = *reinterpret_cast<const float4*>(ws + r * N + c);
+        for (int s = 1; s < slices; ++s) {
+            const float4 v = *reinterpret_cast<const float4*>(ws + s * slice_stride + r * N + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (OUT_FP32) {
+            if (res) {
+                const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(res) + r * ld_res + c);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + r * ld_out + c) = acc;
+        } else {
+            if (res) {
+                const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(res) + r * ld_res + c);
+                const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
+                acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+            }
+            uint2 o;
+            o.x = pack_bf16x2(acc.x, acc.y);
+            o.y = pack_bf16x2(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + r * ld_out + c) = o;
+        }
+    }
+}
+
+extern "C" int pb_splitk_reduce(const float* ws, int slices, long long M, int N, const void* res, long long ld_res, void* out,
+                                long long ld_out, int out_fp32, void* stream) {
+    if (N % 4 || ld_out % 4 || (res && ld_res % 4)) return -1;
+    const unsigned grid = grid_for(M * (N / 4), 256);
+    if (out_fp32) splitk_reduce_kernel<true><<<grid, 256, 0, ST(stream)>>>(ws, slices, M, N, res, ld_res, out, ld_out);
+    else splitk_reduce_kernel<false><<<grid, 256, 0, ST(stream)>>>(ws, slices, M, N, res, ld_res, out, ld_out);
+    return CHECK_LAUNCH();
+}

@@ -210,7 +210,9 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs) {
+        for (int item = pair; item < p.num_items && ok; item += n_pairs) {
+            const int tile = item % p.num_tiles, slice = item / p.num_tiles;
+            const int kb0 = slice * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
             const int m0 = (tile / p.tiles_n) * 256 + int(rank) * 128;     // my half of the A rows
             // my half of the B rows; with the SwiGLU epilogue the halves are the gate rows and the matching up rows
             const int n0 = EPI == GEMM_EPI_SWIGLU ? (tile % p.tiles_n) * 128 + int(rank) * p.epi_i0
@@ -231,7 +233,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 if (!ok) break;
                 fence_proxy_async_global();      // generic-proxy stores of the gather -> async-proxy (TMA) reads
             }
-            for (int kb = 0; kb < num_kb; ++kb) {
+            for (int kb = kb0; kb < kb1; ++kb) {
                 ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -269,16 +271,16 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
             int stage = 0, local = 0;
             uint32_t phase = 0;
             bool ok = true, ready = false;
-            const int my_tiles = p.num_tiles > pair ? (p.num_tiles - pair + n_pairs - 1) / n_pairs : 0;
-            const long long total_kb = (long long)my_tiles * num_kb;
-            long long done_kb = 0;
-            for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs, ++local) {
+            for (int item = pair; item < p.num_items && ok; item += n_pairs, ++local) {
+                const int slice = item / p.num_tiles;
+                const int kb0 = slice * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+                const bool last_item = item + n_pairs >= p.num_items;
                 const int acc = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
                 ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
                 const uint32_t d_tmem = tmem_base + acc * G2_BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!ready) {
                         ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
                         if (!ok) break;
@@ -290,10 +292,9 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     const uint64_t db = B_MN ? umma_smem_desc(sb, BK * 128, 1024) : umma_smem_desc(sb, 16, 1024);
                     const int nstage = stage + 1 == G2_STAGES ? 0 : stage + 1;
                     const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
-                    ++done_kb;
-                    ready = umma2_kblock<A_MN, B_MN>(d_tmem, da, db, idesc, kb != 0, bar_empty + 8 * stage,
-                                                     bar_tfull + 8 * acc, kb == num_kb - 1, bar_full + 8 * nstage, nphase,
-                                                     done_kb < total_kb);
+                    ready = umma2_kblock<A_MN, B_MN>(d_tmem, da, db, idesc, kb != kb0, bar_empty + 8 * stage,
+                                                     bar_tfull + 8 * acc, kb == kb1 - 1, bar_full + 8 * nstage, nphase,
+                                                     !(last_item && kb == kb1 - 1));
                     stage = nstage;
                     phase = nphase;
                 }
@@ -353,14 +354,15 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         bool ok = true;
         if constexpr (EPI == GEMM_EPI_DSWIGLU) {
             // gate | up of the first block of the first tile
-            if (et == 0 && pair < p.num_tiles) {
+            if (et == 0 && pair < p.num_items) {
                 const int m0 = (pair / p.tiles_n) * 256 + int(rank) * 128, n0 = (pair % p.tiles_n) * G2_BN;
                 mbar_expect_tx(bar_eload, 2 * G2_BOX_BYTES);
                 tma_load_2d(s_epi, &em.aux, bar_eload, n0, m0);
                 tma_load_2d(s_epi + G2_BOX_BYTES, &em.aux, bar_eload, p.epi_i0 + n0, m0);
             }
         }
-        for (int tile = pair; tile < p.num_tiles && ok; tile += n_pairs, ++local) {
+        for (int item = pair; item < p.num_items && ok; item += n_pairs, ++local) {
+            const int tile = item % p.num_tiles, slice = item / p.num_tiles;
             const int acc = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             const int m0 = (tile / p.tiles_n) * 256 + int(rank) * 128;
@@ -526,12 +528,14 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 }
             } else {
                 const int cbeg = half * 128;
+                GemmParams ps = p;
+                if (slice) ps.C = reinterpret_cast<float*>(p.C) + slice * p.split_stride;   // split-K partials are fp32
 #pragma unroll 1
                 for (int c = cbeg; c < cbeg + 128; c += 32) {
                     uint32_t v[32];
                     tmem_ld32(t_row + c, v);
                     tmem_ld_wait();
-                    gemm_store_chunk(p, v, row, n0 + c);
+                    gemm_store_chunk(ps, v, row, n0 + c);
                 }
                 release_acc();
             }
@@ -560,9 +564,15 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
     const int tiles_m = (p.M + 255) / 256;
     p.tiles_n = EPI == GEMM_EPI_SWIGLU ? p.epi_i0 / 128 : (p.N + G2_BN - 1) / G2_BN;
     p.num_tiles = tiles_m * p.tiles_n;
+    if (p.num_items <= 0) {   // no split-K requested
+        p.num_items = p.num_tiles;
+        p.kb_per_split = (p.K + BK - 1) / BK;
+    } else {
+        p.num_items *= p.num_tiles;   // the caller passed the number of K slices
+    }
     int ctas = sm_count() & ~1;
     if (max_ctas > 0 && ctas > (max_ctas & ~1)) ctas = max_ctas & ~1;
-    if (ctas > 2 * p.num_tiles) ctas = 2 * p.num_tiles;
+    if (ctas > 2 * p.num_items) ctas = 2 * p.num_items;
     if (ctas < 2) ctas = 2;
     kern<<<ctas, 320, G2_SMEM_BYTES, st>>>(tmA, tmB, em, p, g);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
@@ -668,4 +678,43 @@ extern "C" int pb_gemm_bf16_allgather(const void* A, void* const* shards, void* 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     return a_mn ? launch_gemm_pair<true, false, true>(tmA, tmB, p, max_ctas, st, g)
                 : launch_gemm_pair<false, false, true>(tmA, tmB, p, max_ctas, st, g);
+}
+
+// Split-K form for products with few output tiles and a long K (weight gradients): `slices` K ranges per
+// tile run as separate work items and leave fp32 partial tiles in ws[slices][M][N]; pb_splitk_reduce
+// then sums them (plus an optional addend) into the real output. Deterministic: no atomics.
+extern "C" int pb_gemm_bf16_pair_splitk(const void* A, const void* B, float* ws, int M, int N, int K, long long lda, long long ldb,
+                                        int a_mn, int b_mn, int slices, int max_ctas, int* status, void* stream) {
+    using namespace pb;
+    if (M <= 0 || N <= 0 || K <= 0 || slices < 1) return 0;
+    if ((lda % 8) || (ldb % 8) || (N % 4) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+        (reinterpret_cast<uintptr_t>(ws) & 15))
+        return -1;
+    CUtensorMap tmA, tmB;
+    int rc;
+    if (!a_mn) rc = make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, 128);
+    else       rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
+    if (rc) return rc;
+    if (!b_mn) rc = make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, 128);
+    else       rc = make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
+    if (rc) return rc;
+    const int num_kb = (K + BK - 1) / BK;
+    const int kb_per = (num_kb + slices - 1) / slices;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K; p.C = ws; p.R = nullptr; p.ldc = N; p.ldr = 0; p.out_fp32 = 1; p.status = status;
+    p.num_items = (num_kb + kb_per - 1) / kb_per;      // slices that really have k-blocks
+    p.kb_per_split = kb_per;
+    p.split_stride = (long long)M * N;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, p, max_ctas, st);
+    if (!a_mn && b_mn)  return launch_gemm_pair<false, true>(tmA, tmB, p, max_ctas, st);
+    if (a_mn && !b_mn)  return launch_gemm_pair<true, false>(tmA, tmB, p, max_ctas, st);
+    return launch_gemm_pair<true, true>(tmA, tmB, p, max_ctas, st);
+}
+
+// number of K slices pb_gemm_bf16_pair_splitk will really use for this K and requested count
+extern "C" int pb_gemm_splitk_slices(int K, int slices) {
+    const int num_kb = (K + pb::BK - 1) / pb::BK;
+    const int kb_per = (num_kb + slices - 1) / slices;
+    return (num_kb + kb_per - 1) / kb_per;
 }

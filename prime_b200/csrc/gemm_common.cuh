@@ -17,6 +17,10 @@ struct GemmParams {
     int out_fp32;
     int* status;
     int num_tiles, tiles_n;
+    // split-K: work item w = slice * num_tiles + tile; slice s covers k-blocks [s * kb_per_split, ...) and
+    // stores its fp32 partial tile at C + s * split_stride elements (plain direct-store epilogue only)
+    int num_items, kb_per_split;
+    long long split_stride;
     // fused epilogues of the CTA-pair kernel (GEMM_EPI_*); 0 = plain store
     int epi, epi_i0, epi_i1, epi_i2;
     int staged;      // plain / RoPE epilogue: 1 = stage the bf16 tile in shared memory and store it with TMA

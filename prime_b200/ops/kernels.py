@@ -80,6 +80,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, resi
     # bn: 0 = choose; 128 / 256 = single-CTA tile width; 512 = the CTA-pair (cta_group::2) 256x256 kernel
     use_pair = bn == 512 or (bn == 0 and _GEMM_PAIR and M >= 512 and N >= 256)
     if use_pair:
+        slices = _splitk_slices(M, N, K, a.device) if bn == 0 else 1
+        if slices > 1:
+            # few output tiles, long K (weight gradients): K slices as extra work items, fp32 partials, one reduce
+            ws = _splitk_ws(slices * M * N, a.device)
+            rc = native.cuda().pb_gemm_bf16_pair_splitk(ptr(a), ptr(b), ptr(ws), M, N, K, a.stride(0), b.stride(0), int(a_mn),
+                                                        int(b_mn), slices, max_ctas, ptr(status_word(a.device)), stream_ptr())
+            check(rc, f"pb_gemm_bf16_pair_splitk(M={M},N={N},K={K},slices={slices})")
+            used = native.cuda().pb_gemm_splitk_slices(K, slices)
+            rc = native.cuda().pb_splitk_reduce(ptr(ws), used, M, N, ptr(residual), ldr, ptr(out), out.stride(0),
+                                                int(out.dtype == torch.float32), stream_ptr())
+            check(rc, "pb_splitk_reduce")
+            return out
         rc = native.cuda().pb_gemm_bf16_pair(ptr(a), ptr(b), ptr(out), ptr(residual), M, N, K, a.stride(0), b.stride(0),
                                              out.stride(0), ldr, int(a_mn), int(b_mn), int(out.dtype == torch.float32), max_ctas,
                                              ptr(status_word(a.device)), stream_ptr())
@@ -90,6 +102,40 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, resi
         int(out.dtype == torch.float32), bn if bn in (128, 256) else 0, max_ctas, ptr(status_word(a.device)), stream_ptr())
     check(rc, f"pb_gemm_bf16(M={M},N={N},K={K},a_mn={a_mn},b_mn={b_mn})")
     return out
+
+
+_SPLITK_WS: dict = {}
+_N_PAIRS: dict = {}
+
+
+def _splitk_ws(numel: int, device) -> torch.Tensor:
+    t = _SPLITK_WS.get(device)
+    if t is None or t.numel() < numel:
+        t = torch.empty(numel, dtype=torch.float32, device=device)
+        _SPLITK_WS[device] = t
+    return t
+
+
+def _splitk_slices(M: int, N: int, K: int, device) -> int:
+    """K slices for the CTA-pair GEMM: 1 unless the product has too few 256x256 tiles to fill the GPU and a long
+    K. Minimises waves x k-blocks per slice (0.42 us per k-block) plus the fp32 partials' round trip."""
+    if N % 4 or K < 4096:
+        return 1
+    pairs = _N_PAIRS.get(device)
+    if pairs is None:
+        pairs = _N_PAIRS[device] = torch.cuda.get_device_properties(device).multi_processor_count // 2
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    if tiles * 4 > pairs * 3:
+        return 1
+    kb = (K + 63) // 64
+    best, best_t = 1, -(-tiles // pairs) * kb * 0.42
+    for s_ in range(2, 17):
+        if s_ * M * N * 4 > (256 << 20):
+            break
+        t = -(-tiles * s_ // pairs) * -(-kb // s_) * 0.42 + s_ * M * N * 8 / 5e6 + 5.0
+        if t < best_t:
+            best, best_t = s_, t
+    return best
 
 
 def _pair_ok(M: int, N: int) -> bool:

@@ -87,6 +87,29 @@ def test_gemm_fused_rope_epilogue(M, H, KV, hd, K, T):
     assert _rel(out[:, : (H + KV) * hd], (x.float() @ w.float().t())[:, : (H + KV) * hd]) > 0.1
 
 
+@pytest.mark.parametrize("M,N,K,res", [(1024, 1024, 8192, False), (768, 1024, 32768, True), (3072, 1024, 16384, True)])
+def test_gemm_split_k_weight_gradient(M, N, K, res):
+    """Few output tiles + long K: the K slices run as separate work items, partials are reduced in fp32."""
+    torch.manual_seed(0)
+    dev = "cuda"
+    a = torch.randn(K, M, device=dev, dtype=torch.bfloat16)      # dy [tokens, M] read M-major
+    b = torch.randn(K, N, device=dev, dtype=torch.bfloat16)
+    assert ops._splitk_slices(M, N, K, torch.device(dev, torch.cuda.current_device())) > 1
+    ref = a.float().t() @ b.float()
+    for dt in (torch.bfloat16, torch.float32):
+        r = torch.randn(M, N, device=dev, dtype=dt) if res else None
+        out = torch.empty(M, N, device=dev, dtype=dt)
+        ops.gemm(a, b, out=out, residual=r, a_mn=True, b_mn=True)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert _rel(out, ref + (r.float() if res else 0)) < (1e-2 if dt == torch.bfloat16 else 1e-3)
+    # accumulate in place (residual aliases the output)
+    acc = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+    want = ref + acc.float()
+    ops.gemm(a, b, out=acc, residual=acc, a_mn=True, b_mn=True)
+    assert _rel(acc, want) < 1e-2
+
+
 def test_gemm_persistent_many_tiles():
     torch.manual_seed(1)
     a = torch.randn(8192, 1024, device="cuda", dtype=torch.bfloat16)
