@@ -416,7 +416,7 @@ extern "C" int pb_rmsnorm_bwd(const void* x, const void* w, const float* rstd, c
     }
 #undef RB
     if (cudaGetLastError() != cudaSuccess) return -30;
-    colsum_partials_kernel<<<(N + 255) / 256, 256, 0, ST(stream)>>>(dw_partial, dw, ctas, N, dw_fp32, dw_accumulate);
+    colsum_partials_kernel<<<(N + 31) / 32, 256, 0, ST(stream)>>>(dw_partial, dw, ctas, N, dw_fp32, dw_accumulate);
     return CHECK_LAUNCH();
 }
 

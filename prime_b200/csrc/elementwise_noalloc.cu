@@ -71,6 +71,6 @@ extern "C" int pb_rmsnorm_bwd_noalloc(const void* x, const void* w, const float*
     if (cudaGetLastError() != cudaSuccess) return PB_NOALLOC_ERR_LAUNCH;
     // every one of the ctas*N partials was just rewritten by the kernel above, so stale contents of
     // the shared array from an earlier call never reach this reduction
-    colsum_partials_kernel<<<(N + 255) / 256, 256, 0, st>>>(partials, dw, ctas, N, dw_fp32, dw_accumulate);
+    colsum_partials_kernel<<<(N + 31) / 32, 256, 0, st>>>(partials, dw, ctas, N, dw_fp32, dw_accumulate);
     return cudaGetLastError() == cudaSuccess ? 0 : PB_NOALLOC_ERR_LAUNCH;
 }

@@ -107,19 +107,38 @@ __global__ void __launch_bounds__(256, (NCH <= 4 ? 2 : 1)) rmsnorm_bwd_kernel(co
     }
 }
 
-// dw[c] (+)= sum_b partial[b, c]  (fixed order); output bf16 or fp32
-static __global__ void colsum_partials_kernel(const float* __restrict__ partial, void* __restrict__ out, int nb, int N,
-                                       int out_fp32, int accumulate) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= N) return;
-    float s = 0.f;
-    for (int b = 0; b < nb; ++b) s += partial[(long long)b * N + c];
-    if (out_fp32) {
-        float* o = reinterpret_cast<float*>(out);
-        o[c] = accumulate ? o[c] + s : s;
-    } else {
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
-        o[c] = __float2bfloat16(accumulate ? __bfloat162float(o[c]) + s : s);
+// dw[c] (+)= sum_b partial[b, c]; output bf16 or fp32. One block = 32 columns x 8 row groups: every thread
+// sums the rows b = g, g + 8, ... of its column with four loads in flight, the eight group sums are then
+// added in a fixed order (deterministic for a given number of partial rows).
+static __global__ void __launch_bounds__(256) colsum_partials_kernel(const float* __restrict__ partial, void* __restrict__ out,
+                                                                     int nb, int N, int out_fp32, int accumulate) {
+    __shared__ float red[8][33];
+    const int cx = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    if (c < N) {
+        int b = g;
+        for (; b + 24 < nb; b += 32) {
+            s0 += partial[(long long)b * N + c];
+            s1 += partial[(long long)(b + 8) * N + c];
+            s2 += partial[(long long)(b + 16) * N + c];
+            s3 += partial[(long long)(b + 24) * N + c];
+        }
+        for (; b < nb; b += 8) s0 += partial[(long long)b * N + c];
+    }
+    red[g][cx] = (s0 + s1) + (s2 + s3);
+    __syncthreads();
+    if (g == 0 && c < N) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += red[k][cx];
+        if (out_fp32) {
+            float* o = reinterpret_cast<float*>(out);
+            o[c] = accumulate ? o[c] + s : s;
+        } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+            o[c] = __float2bfloat16(accumulate ? __bfloat162float(o[c]) + s : s);
+        }
     }
 }
 
