@@ -275,7 +275,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--micro-bs", type=int, default=32)
     ap.add_argument("--ref-micro-bs", type=int, default=64)  # the reference's own 150M config uses 64 (configs/150M/H100.toml)
-    ap.add_argument("--ce-chunk", type=int, default=8192)
+    ap.add_argument("--ce-chunk", type=int, default=32768)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     world_env = int(os.environ.get("WORLD_SIZE", "1"))

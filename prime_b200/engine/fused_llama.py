@@ -85,7 +85,7 @@ class FusedLlama:
     """See module docstring. One instance per process / GPU."""
 
     def __init__(self, args: ModelArgs, device: torch.device | str = "cuda", comm=None, grad_dtype=torch.bfloat16,
-                 ac_ckpt: bool | int = False, ce_chunk_tokens: int = 8192, z_mode: int = K.Z_NONE, z_weight: float = 0.0,
+                 ac_ckpt: bool | int = False, ce_chunk_tokens: int = 32768, z_mode: int = K.Z_NONE, z_weight: float = 0.0,
                  comm_ctas: int = 148):
         self.args = args
         self.device = torch.device(device)
