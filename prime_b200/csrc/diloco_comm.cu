@@ -66,11 +66,31 @@ __global__ void __launch_bounds__(DL_THREADS) dl_sumsq_kernel(const float* __res
     const int sub = blockIdx.x % DL_BLOCKS_PER_CHUNK;
     const long long lo = chunk * DL_CHUNK, hi = min(n, lo + (long long)DL_CHUNK);
     float s = 0.f;
-    for (long long i = lo + sub * DL_THREADS + threadIdx.x; i < hi; i += DL_BLOCKS_PER_CHUNK * DL_THREADS) {
-        float v;
-        if (MODE == 0) v = fake ? 0.f : (b ? a[i] - b[i] : a[i]) * inv_w;
-        else v = a[i - first_chunk * DL_CHUNK];
-        s += v * v;
+    const long long off = MODE == 0 ? 0 : first_chunk * DL_CHUNK;
+    // chunk starts are multiples of 4 elements, so float4 loads are aligned whenever the base pointers are
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+    for (long long i = lo + (sub * DL_THREADS + threadIdx.x) * 4ll; i < hi; i += DL_BLOCKS_PER_CHUNK * DL_THREADS * 4ll) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (aligned && i + 3 < hi) {
+            if (!(MODE == 0 && fake)) {
+                const float4 x = *reinterpret_cast<const float4*>(a + i - off);
+                v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+                if (MODE == 0) {
+                    if (b) {
+                        const float4 y = *reinterpret_cast<const float4*>(b + i);
+                        v[0] -= y.x; v[1] -= y.y; v[2] -= y.z; v[3] -= y.w;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) v[k] *= inv_w;
+                }
+            }
+        } else {
+            for (int k = 0; k < 4 && i + k < hi; ++k) {
+                if (MODE == 0) v[k] = fake ? 0.f : (b ? a[i + k] - b[i + k] : a[i + k]) * inv_w;
+                else v[k] = a[i + k - off];
+            }
+        }
+        s += (v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3]);
     }
     s = block_sum(s, red);
     if (threadIdx.x == 0) partial[blockIdx.x] = s;
@@ -96,31 +116,85 @@ __global__ void __launch_bounds__(DL_THREADS) dl_quantize_kernel(const float* __
                                                                  int fake, long long n, long long first_chunk,
                                                                  const float* __restrict__ sumsq_partial, uint8_t* __restrict__ q,
                                                                  long long* __restrict__ bin_sum, unsigned* __restrict__ bin_cnt) {
-    __shared__ unsigned long long s_sum[256];
-    __shared__ unsigned s_cnt[256];
+    // One shared-memory atomic per element: an inner bin b holds (count << 40) | sum of the fixed-point
+    // offsets of its values from the bin's lower edge (b - 128.5), which lie in [0, 2^20]; at most 65536
+    // elements of a chunk reach one block, so neither field can overflow. The two clamping end bins take
+    // values from an unbounded range and keep an exact 64-bit sum and a count of their own.
+    constexpr int COPIES = 8;                       // histogram copies: two warps share one
+    __shared__ unsigned long long s_sum[COPIES][256];
+    __shared__ unsigned long long s_edge_sum[2];
+    __shared__ unsigned s_edge_cnt[2];
     const int cb = blockIdx.x / DL_BLOCKS_PER_CHUNK;
     const long long chunk = first_chunk + cb;
     const int sub = blockIdx.x % DL_BLOCKS_PER_CHUNK;
     const long long lo = chunk * DL_CHUNK, hi = min(n, lo + (long long)DL_CHUNK);
-    if (threadIdx.x < 256) { s_sum[threadIdx.x] = 0ull; s_cnt[threadIdx.x] = 0u; }
+    for (int i = threadIdx.x; i < COPIES * 256; i += DL_THREADS) (&s_sum[0][0])[i] = 0ull;
+    if (threadIdx.x < 2) { s_edge_sum[threadIdx.x] = 0ull; s_edge_cnt[threadIdx.x] = 0u; }
     const float inv_scale = 1.f / dl_chunk_scale(sumsq_partial, cb, hi - lo);
     __syncthreads();
-    for (long long i = lo + sub * DL_THREADS + threadIdx.x; i < hi; i += DL_BLOCKS_PER_CHUNK * DL_THREADS) {
-        float v;
-        if (MODE == 0) v = fake ? 0.f : (b ? a[i] - b[i] : a[i]) * inv_w;
-        else v = a[i - first_chunk * DL_CHUNK];
-        const float t = v * inv_scale;
-        int qi = __float2int_rn(roundf(t)) + 128;       // roundf: half away from zero
-        qi = max(0, min(255, qi));
-        q[i] = uint8_t(qi);
-        const long long fx = __float2ll_rn(fminf(fmaxf(t, -1.0e6f), 1.0e6f) * DL_FX);
-        atomicAdd(&s_sum[qi], static_cast<unsigned long long>(fx));   // two's complement: wraps correctly for negatives
-        atomicAdd(&s_cnt[qi], 1u);
+    unsigned long long* my_sum = s_sum[(threadIdx.x >> 6) % COPIES];
+    const long long off = MODE == 0 ? 0 : first_chunk * DL_CHUNK;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0;
+    for (long long i = lo + (sub * DL_THREADS + threadIdx.x) * 4ll; i < hi; i += DL_BLOCKS_PER_CHUNK * DL_THREADS * 4ll) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        const bool full = aligned && i + 3 < hi;
+        if (full) {
+            if (!(MODE == 0 && fake)) {
+                const float4 x = *reinterpret_cast<const float4*>(a + i - off);
+                v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+                if (MODE == 0) {
+                    if (b) {
+                        const float4 y = *reinterpret_cast<const float4*>(b + i);
+                        v[0] -= y.x; v[1] -= y.y; v[2] -= y.z; v[3] -= y.w;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) v[k] *= inv_w;
+                }
+            }
+        } else {
+            for (int k = 0; k < 4 && i + k < hi; ++k) {
+                if (MODE == 0) v[k] = fake ? 0.f : (b ? a[i + k] - b[i + k] : a[i + k]) * inv_w;
+                else v[k] = a[i + k - off];
+            }
+        }
+        uint32_t packed = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (full || i + k < hi) {
+                const float t = v[k] * inv_scale;
+                int qi = __float2int_rn(roundf(t)) + 128;       // roundf: half away from zero
+                qi = max(0, min(255, qi));
+                packed |= uint32_t(qi) << (8 * k);
+                const long long fx = __float2ll_rn(fminf(fmaxf(t, -1.0e6f), 1.0e6f) * DL_FX);
+                if (qi > 0 && qi < 255) {
+                    const long long edge = static_cast<long long>(2 * qi - 257) << 19;        // (qi - 128.5) * 2^20
+                    atomicAdd(&my_sum[qi], (1ull << 40) | static_cast<unsigned long long>(fx - edge));
+                } else {
+                    atomicAdd(&s_edge_sum[qi ? 1 : 0], static_cast<unsigned long long>(fx));   // two's complement: wraps correctly for negatives
+                    atomicAdd(&s_edge_cnt[qi ? 1 : 0], 1u);
+                }
+            }
+        }
+        if (full) *reinterpret_cast<uint32_t*>(q + i) = packed;     // q + chunk start is 4-byte aligned
+        else for (int k = 0; k < 4 && i + k < hi; ++k) q[i + k] = uint8_t(packed >> (8 * k));
     }
     __syncthreads();
     if (threadIdx.x < 256) {
-        bin_sum[(long long)blockIdx.x * 256 + threadIdx.x] = static_cast<long long>(s_sum[threadIdx.x]);
-        bin_cnt[(long long)blockIdx.x * 256 + threadIdx.x] = s_cnt[threadIdx.x];
+        const int b = threadIdx.x;
+        long long ssum;
+        unsigned scnt;
+        if (b > 0 && b < 255) {
+            unsigned long long packed = 0ull;
+#pragma unroll
+            for (int c = 0; c < COPIES; ++c) packed += s_sum[c][b];      // integer sums: order-free
+            scnt = unsigned(packed >> 40);
+            ssum = static_cast<long long>(packed & ((1ull << 40) - 1)) + static_cast<long long>(scnt) * (static_cast<long long>(2 * b - 257) << 19);
+        } else {
+            ssum = static_cast<long long>(s_edge_sum[b ? 1 : 0]);
+            scnt = s_edge_cnt[b ? 1 : 0];
+        }
+        bin_sum[(long long)blockIdx.x * 256 + b] = ssum;
+        bin_cnt[(long long)blockIdx.x * 256 + b] = scnt;
     }
 }
 
@@ -194,15 +268,34 @@ __global__ void __launch_bounds__(DL_THREADS) dl_gather_nesterov_kernel(DlPeers 
     if (threadIdx.x < 256) s_lut[threadIdx.x] = p.lut2[owner][chunk * 256 + threadIdx.x];
     __syncthreads();
     const uint8_t* src = p.q2[owner];
-    for (long long i = lo + sub * DL_THREADS + threadIdx.x; i < hi; i += DL_BLOCKS_PER_CHUNK * DL_THREADS) {
-        const float g = s_lut[src[i]];
-        if (g_out) g_out[i] = g;
-        if (outer) {
-            const float m = mu * mom[i] + g;
-            mom[i] = m;
-            const float o = outer[i] - lr * (g + mu * m);
-            outer[i] = o;
-            inner[i] = o;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(outer) | reinterpret_cast<uintptr_t>(inner) | reinterpret_cast<uintptr_t>(mom) |
+                           reinterpret_cast<uintptr_t>(g_out)) & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 3) == 0;
+    for (long long i = lo + (sub * DL_THREADS + threadIdx.x) * 4ll; i < hi; i += DL_BLOCKS_PER_CHUNK * DL_THREADS * 4ll) {
+        if (aligned && i + 3 < hi) {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(src + i);
+            const float4 g = make_float4(s_lut[w & 255], s_lut[(w >> 8) & 255], s_lut[(w >> 16) & 255], s_lut[w >> 24]);
+            if (g_out) *reinterpret_cast<float4*>(g_out + i) = g;
+            if (outer) {
+                float4 m = *reinterpret_cast<const float4*>(mom + i);
+                float4 o = *reinterpret_cast<const float4*>(outer + i);
+                m.x = mu * m.x + g.x; m.y = mu * m.y + g.y; m.z = mu * m.z + g.z; m.w = mu * m.w + g.w;
+                o.x -= lr * (g.x + mu * m.x); o.y -= lr * (g.y + mu * m.y); o.z -= lr * (g.z + mu * m.z); o.w -= lr * (g.w + mu * m.w);
+                *reinterpret_cast<float4*>(mom + i) = m;
+                *reinterpret_cast<float4*>(outer + i) = o;
+                *reinterpret_cast<float4*>(inner + i) = o;
+            }
+        } else {
+            for (long long j = i; j < min(hi, i + 4); ++j) {
+                const float g = s_lut[src[j]];
+                if (g_out) g_out[j] = g;
+                if (outer) {
+                    const float m = mu * mom[j] + g;
+                    mom[j] = m;
+                    const float o = outer[j] - lr * (g + mu * m);
+                    outer[j] = o;
+                    inner[j] = o;
+                }
+            }
         }
     }
 }
