@@ -568,7 +568,8 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
 
 }  // namespace pb
 
-// dq_acc: fp32 [M, H*HD] scratch (zeroed here); D: fp32 [H, M] scratch. Writes all of dqkv.
+// dq_acc: fp32 [M, H*HD] scratch (zeroed here); D: fp32 [H, M] scratch, computed here from o and dout unless o is
+// null (then the caller has already filled it). Writes all of dqkv.
 // rope_table != null: the inverse rotation is applied to dq and dk on the way out.
 extern "C" int pb_attn_bwd(const void* qkv, const void* o, const void* dout, const float* lse2, const int* seq_start,
                            void* dqkv, float* dq_acc, float* D, const float* rope_table, int T, int M, int H, int KV, int HD,
@@ -587,7 +588,7 @@ extern "C" int pb_attn_bwd(const void* qkv, const void* o, const void* dout, con
     rc = make_tmap_f32_2d(&tdq, dq_acc, uint64_t(H) * HD, M, uint64_t(H) * HD, 32, 32);
     if (rc) return rc;
     if (cudaMemsetAsync(dq_acc, 0, size_t(M) * H * HD * sizeof(float), st) != cudaSuccess) return -40;
-    {
+    if (o) {   // o == null: the caller already filled D
         const long long rows = (long long)M * H;
         const int rows_per_block = 256 / (HD / 8);
         long long blocks = (rows + 4LL * rows_per_block - 1) / (4LL * rows_per_block);

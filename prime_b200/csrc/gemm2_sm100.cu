@@ -345,7 +345,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // whole 128-byte rows instead of 64-byte pieces 32 rows apart; the fused SwiGLU backward also
         // fetches its inputs that way, one block ahead. fp32 outputs and residual adds use direct stores.
         const int et = threadIdx.x - 64;                           // 0..255 within the eight epilogue warps
-        const bool staged = EPI == GEMM_EPI_SWIGLU || EPI == GEMM_EPI_DSWIGLU || p.staged;
+        const bool staged = EPI == GEMM_EPI_SWIGLU || EPI == GEMM_EPI_DSWIGLU || EPI == GEMM_EPI_ROWDOT || p.staged;
         auto epi_sync = [] { asm volatile("bar.sync 2, 256;" ::: "memory"); };
         // this thread's 64-byte piece (32 bf16 = chunks ch0..ch0+3 of 16 bytes) of row r in a staging box
         auto box_off = [&](int box, int ch) { return box * G2_BOX_BYTES + row_in_half * 128 + (((ch) ^ (row_in_half & 7)) << 4); };
@@ -359,6 +359,15 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 mbar_expect_tx(bar_eload, 2 * G2_BOX_BYTES);
                 tma_load_2d(s_epi, &em.aux, bar_eload, n0, m0);
                 tma_load_2d(s_epi + G2_BOX_BYTES, &em.aux, bar_eload, p.epi_i0 + n0, m0);
+            }
+        }
+        if constexpr (EPI == GEMM_EPI_ROWDOT) {
+            // the two 64-column boxes of the other matrix for the first round of the first tile
+            if (et == 0 && pair < p.num_items) {
+                const int m0 = (pair / p.tiles_n) * 256 + int(rank) * 128, n0 = (pair % p.tiles_n) * G2_BN;
+                mbar_expect_tx(bar_eload, 2 * G2_BOX_BYTES);
+                tma_load_2d(s_epi, &em.aux, bar_eload, n0, m0);
+                tma_load_2d(s_epi + G2_BOX_BYTES, &em.aux, bar_eload, n0 + 64, m0);
             }
         }
         for (int item = pair; item < p.num_items && ok; item += n_pairs, ++local) {
@@ -474,6 +483,63 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         tma_store_commit();
                     }
                 }
+            } else if constexpr (EPI == GEMM_EPI_ROWDOT) {
+                // two rounds of 128 columns; buffer b = boxes 2b, 2b+1 arrive holding the other matrix and leave
+                // holding C; this warp owns box `half` of the round = the 64 columns of one head of its row
+#pragma unroll 1
+                for (int rnd = 0; rnd < 2; ++rnd, ++rounds) {
+                    const int buf = rounds & 1;
+                    uint32_t v0[32], v1[32];
+                    tmem_ld32(t_row + rnd * 128 + half * 64, v0);
+                    tmem_ld32(t_row + rnd * 128 + half * 64 + 32, v1);
+                    if (et == 0) {
+                        int nt = tile, nr = rnd + 1;
+                        if (nr == 2) { nr = 0; nt += n_pairs; }
+                        if (nt < p.num_tiles) {
+                            const int nm0 = (nt / p.tiles_n) * 256 + int(rank) * 128, nn0 = (nt % p.tiles_n) * G2_BN + nr * 128;
+                            tma_store_wait_read<0>();      // the stores that last used that buffer have read it
+                            mbar_expect_tx(bar_eload + 8 * (buf ^ 1), 2 * G2_BOX_BYTES);   // columns past N arrive as zeros
+                            tma_load_2d(s_epi + (2 * (buf ^ 1)) * G2_BOX_BYTES, &em.aux, bar_eload + 8 * (buf ^ 1), nn0, nm0);
+                            tma_load_2d(s_epi + (2 * (buf ^ 1) + 1) * G2_BOX_BYTES, &em.aux, bar_eload + 8 * (buf ^ 1), nn0 + 64, nm0);
+                        }
+                    }
+                    ok = mbar_wait(bar_eload + 8 * buf, (rounds >> 1) & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
+                    ok = __all_sync(0xffffffffu, ok);
+                    tmem_ld_wait();
+                    if (rnd == 1) release_acc();
+                    if (!ok) break;
+                    const int cb = n0 + rnd * 128 + half * 64;
+                    float dot = 0.f;
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        uint32_t (&v)[32] = hh ? v1 : v0;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4* px = reinterpret_cast<uint4*>(g_epi + box_off(2 * buf + half, hh * 4 + q));
+                            const uint4 x = *px;
+                            const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+                            uint32_t o[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                const float2 x2 = unpack_bf16x2(xw[t]);
+                                const float c0 = __uint_as_float(v[8 * q + 2 * t]), c1 = __uint_as_float(v[8 * q + 2 * t + 1]);
+                                dot += c0 * x2.x + c1 * x2.y;
+                                o[t] = pack_bf16x2(c0, c1);
+                            }
+                            *px = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    }
+                    if (row < p.M && cb < p.N) reinterpret_cast<float*>(p.aux2)[(long long)(cb / 64) * p.M + row] = dot;
+                    fence_proxy_async_smem();
+                    epi_sync();
+                    if (et == 0) {
+#pragma unroll
+                        for (int h2 = 0; h2 < 2; ++h2)
+                            if (n0 + rnd * 128 + h2 * 64 < p.N)
+                                tma_store_2d(&em.c, s_epi + (2 * buf + h2) * G2_BOX_BYTES, n0 + rnd * 128 + h2 * 64, m0);
+                        tma_store_commit();
+                    }
+                }
             } else if (staged) {
                 // two rounds of 128 columns; buffer b = boxes 2b, 2b+1; this warp fills box `half` of the round
                 constexpr bool rope = EPI == GEMM_EPI_ROPE;
@@ -582,25 +648,26 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
 
 extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
                                      long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_fp32, int max_ctas,
-                                     int epi, int epi_i0, int epi_i1, int epi_i2, void* aux, long long ldaux, int* status,
-                                     void* stream);
+                                     int epi, int epi_i0, int epi_i1, int epi_i2, void* aux, long long ldaux, void* aux2,
+                                     int* status, void* stream);
 
 // Same contract as pb_gemm_bf16; requires nothing more of the operands. Tile 256 x 256 per CTA pair.
 extern "C" int pb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
                                  long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_fp32, int max_ctas,
                                  int* status, void* stream) {
     return pb_gemm_bf16_pair_epi(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, out_fp32, max_ctas, 0, 0, 0, 0, nullptr, 0,
-                                 status, stream);
+                                 nullptr, status, stream);
 }
 
 // pb_gemm_bf16_pair with one of the fused epilogues described next to GEMM_EPI_* (bf16 output only):
 //   epi 1 (SwiGLU)  : B = [w1; w3] K-major, N = 2F, epi_i0 = F (multiple of 128), C = h13, aux = act, ldaux its pitch
 //   epi 2 (RoPE)    : epi_i0 = T, epi_i1 = number of leading columns to rotate, epi_i2 = head size, aux = fp32 table
 //   epi 3 (dSwiGLU) : N = F = epi_i0, aux = h13 (read gate | up, written d gate | d up), C unused
+//   epi 4 (row dot) : aux = bf16 [M, N] with pitch ldaux, epi_i0 = 64 columns per group, aux2 = fp32 [N / 64, M]
 extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
                                      long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_fp32, int max_ctas,
-                                     int epi, int epi_i0, int epi_i1, int epi_i2, void* aux, long long ldaux, int* status,
-                                     void* stream) {
+                                     int epi, int epi_i0, int epi_i1, int epi_i2, void* aux, long long ldaux, void* aux2,
+                                     int* status, void* stream) {
     using namespace pb;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (epi != GEMM_EPI_NONE) {
@@ -608,7 +675,8 @@ extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, cons
         if (epi == GEMM_EPI_SWIGLU && (a_mn || b_mn || epi_i0 % 128 || N != 2 * epi_i0 || ldaux % 8)) return -4;
         if (epi == GEMM_EPI_ROPE && (a_mn || b_mn || epi_i0 <= 0 || epi_i2 % 64 || epi_i1 % 64 || epi_i1 > N)) return -4;
         if (epi == GEMM_EPI_DSWIGLU && (a_mn || !b_mn || N != epi_i0 || epi_i0 % 64 || ldaux % 8)) return -4;
-        if (epi < 0 || epi > GEMM_EPI_DSWIGLU) return -4;
+        if (epi == GEMM_EPI_ROWDOT && (a_mn || epi_i0 != 64 || ldaux % 8 || !aux2)) return -4;
+        if (epi < 0 || epi > GEMM_EPI_ROWDOT) return -4;
     }
     if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
     const int vec = out_fp32 ? 4 : 8;
@@ -623,7 +691,7 @@ extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, cons
     if (rc) return rc;
     GemmParams p{};
     p.M = M; p.N = N; p.K = K; p.C = C; p.R = R; p.ldc = ldc; p.ldr = ldr; p.out_fp32 = out_fp32; p.status = status;
-    p.epi = epi; p.epi_i0 = epi_i0; p.epi_i1 = epi_i1; p.epi_i2 = epi_i2; p.aux = aux; p.ldaux = ldaux;
+    p.epi = epi; p.epi_i0 = epi_i0; p.epi_i1 = epi_i1; p.epi_i2 = epi_i2; p.aux = aux; p.ldaux = ldaux; p.aux2 = aux2;
     // bf16 tiles without a residual leave through shared memory + TMA stores
     p.staged = (!out_fp32 && !R && epi != GEMM_EPI_DSWIGLU) ? 1 : 0;
     EpiMaps em{};
@@ -633,12 +701,15 @@ extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, cons
     }
     if (epi == GEMM_EPI_SWIGLU) rc = make_tmap_bf16_2d(&em.aux, aux, epi_i0, M, ldaux, 64, 128);
     if (epi == GEMM_EPI_DSWIGLU) rc = make_tmap_bf16_2d(&em.aux, aux, 2 * uint64_t(epi_i0), M, ldaux, 64, 128);
+    if (epi == GEMM_EPI_ROWDOT) rc = make_tmap_bf16_2d(&em.aux, aux, N, M, ldaux, 64, 128);
     if (rc) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const GatherParams ng{};
     if (epi == GEMM_EPI_SWIGLU) return launch_gemm_pair<false, false, false, GEMM_EPI_SWIGLU>(tmA, tmB, p, max_ctas, st, ng, em);
     if (epi == GEMM_EPI_ROPE) return launch_gemm_pair<false, false, false, GEMM_EPI_ROPE>(tmA, tmB, p, max_ctas, st, ng, em);
     if (epi == GEMM_EPI_DSWIGLU) return launch_gemm_pair<false, true, false, GEMM_EPI_DSWIGLU>(tmA, tmB, p, max_ctas, st, ng, em);
+    if (epi == GEMM_EPI_ROWDOT && b_mn) return launch_gemm_pair<false, true, false, GEMM_EPI_ROWDOT>(tmA, tmB, p, max_ctas, st, ng, em);
+    if (epi == GEMM_EPI_ROWDOT) return launch_gemm_pair<false, false, false, GEMM_EPI_ROWDOT>(tmA, tmB, p, max_ctas, st, ng, em);
     if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, p, max_ctas, st, ng, em);
     if (!a_mn && b_mn)  return launch_gemm_pair<false, true>(tmA, tmB, p, max_ctas, st, ng, em);
     if (a_mn && !b_mn)  return launch_gemm_pair<true, false>(tmA, tmB, p, max_ctas, st, ng, em);

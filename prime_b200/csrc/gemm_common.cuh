@@ -26,6 +26,7 @@ struct GemmParams {
     int staged;      // plain / RoPE epilogue: 1 = stage the bf16 tile in shared memory and store it with TMA
     void* aux;
     long long ldaux;
+    void* aux2;
 };
 
 // Epilogues fused into the CTA-pair GEMM:
@@ -37,7 +38,10 @@ struct GemmParams {
 //           position = row % epi_i0, aux = fp32 table [T, hd/2, 2] of (cos, sin)) before the store.
 //  DSWIGLU: the product is d(act) [M, F = epi_i0]; aux = h13 [M, 2F] holds gate | up and is overwritten
 //           in place with d(gate) | d(up). Nothing is written to C.
-constexpr int GEMM_EPI_NONE = 0, GEMM_EPI_SWIGLU = 1, GEMM_EPI_ROPE = 2, GEMM_EPI_DSWIGLU = 3;
+//  ROWDOT : besides the plain bf16 store of C, aux2[(col / epi_i0) * M + row] = sum over the epi_i0 (= 64) columns of
+//           one head of C[row, col] * aux[row, col] (fp32 accumulator values times a bf16 matrix of C's shape):
+//           the dO . O row sums that the attention backward needs, taken where dO is produced.
+constexpr int GEMM_EPI_NONE = 0, GEMM_EPI_SWIGLU = 1, GEMM_EPI_ROPE = 2, GEMM_EPI_DSWIGLU = 3, GEMM_EPI_ROWDOT = 4;
 
 __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&f)[32]) {
 #pragma unroll

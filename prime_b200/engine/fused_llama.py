@@ -274,10 +274,14 @@ class FusedLlama:
                       accumulate_dw=self._accum)
         # h = x + o @ wo^T
         do = self._buf("do", (M, H * hd))
-        K.gemm(dh, self.w[pre + "attention.wo.weight"], out=do, b_mn=True)
+        # dO = dh @ wo; the dO . O row sums of the attention backward come out of the same kernel where it applies
+        dots = A.row_dots_buffer(dh.device, M, H) if dh.is_cuda else None
+        if dots is None or not K.gemm_rowdot(dh, self.w[pre + "attention.wo.weight"], do, o, dots, hd, b_mn=True):
+            K.gemm(dh, self.w[pre + "attention.wo.weight"], out=do, b_mn=True)
+            dots = None
         self._wgrad(dh, o, self.g[pre + "attention.wo.weight"])
         dqkv = self._buf("dqkv", (M, (H + 2 * KV) * hd))
-        A.attention_bwd(qkv, o, do, lse2, seq_start, H, KV, hd, dqkv=dqkv, rope_table=self._rope, seq_len=T)
+        A.attention_bwd(qkv, o, do, lse2, seq_start, H, KV, hd, dqkv=dqkv, rope_table=self._rope, seq_len=T, row_dots=dots)
         dxn = self._buf("dxn", (M, D))
         K.gemm(dqkv, self.wqkv[i], out=dxn, b_mn=True)
         self._wgrad(dqkv, xn, self.gqkv[i])

@@ -26,7 +26,7 @@ _CUDA_SIGS = {
     "pb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp, vp],
     "pb_gemm_bf16_pair": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, i32, i32, i32, vp, vp],
     "pb_gemm_bf16_pair_epi": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp, i64,
-                              vp, vp],
+                              vp, vp, vp],
     "pb_gemm_bf16_pair_splitk": [vp, vp, vp, i32, i32, i32, i64, i64, i32, i32, i32, i32, vp, vp],
     "pb_gemm_splitk_slices": [i32, i32],
     "pb_splitk_reduce": [vp, i32, i64, i32, vp, i64, vp, i64, i32, vp],

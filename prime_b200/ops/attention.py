@@ -126,11 +126,18 @@ def attention_fwd(qkv: torch.Tensor, seq_start: torch.Tensor, H: int, KV: int, h
     return out, lse2
 
 
+def row_dots_buffer(device, M: int, H: int) -> torch.Tensor:
+    """fp32 [H * M] scratch for the dO . O row sums (shared with the backward kernel's own pre-pass)."""
+    return _scratch_buf(device, "attn_D", M * H)
+
+
 def attention_bwd(qkv: torch.Tensor, o: torch.Tensor, dout: torch.Tensor, lse2: torch.Tensor, seq_start: torch.Tensor,
                   H: int, KV: int, hd: int, scale: float | None = None, dqkv: torch.Tensor | None = None,
-                  rope_table: torch.Tensor | None = None, seq_len: int = 0):
+                  rope_table: torch.Tensor | None = None, seq_len: int = 0, row_dots: torch.Tensor | None = None):
     """Gradient of the fused qkv buffer. With ``rope_table`` the inverse rotation of dq and dk is
-    folded into the final pass (so the result is the gradient w.r.t. the *unrotated* projection)."""
+    folded into the final pass (so the result is the gradient w.r.t. the *unrotated* projection).
+    ``row_dots`` ([H, M] fp32 = sum over a head's columns of dout * o), when the caller already has it
+    (``kernels.gemm_rowdot``), replaces the kernel's own pre-pass over ``o`` and ``dout``."""
     M = qkv.shape[0]
     scale = scale if scale is not None else hd ** -0.5
     if dqkv is None:
@@ -149,8 +156,8 @@ def attention_bwd(qkv: torch.Tensor, o: torch.Tensor, dout: torch.Tensor, lse2: 
     if hd not in (64, 128):
         return _small_head_bwd(qkv, dout, seq_start, H, KV, hd, scale, dqkv, rope_table, seq_len)
     dq_acc = _scratch_buf(qkv.device, "attn_dq", M * H * hd)
-    D = _scratch_buf(qkv.device, "attn_D", M * H)
-    check(native.cuda().pb_attn_bwd(ptr(qkv), ptr(o), ptr(dout), ptr(lse2), ptr(seq_start), ptr(dqkv), ptr(dq_acc), ptr(D),
+    D = row_dots if row_dots is not None else _scratch_buf(qkv.device, "attn_D", M * H)
+    check(native.cuda().pb_attn_bwd(ptr(qkv), ptr(o) if row_dots is None else None, ptr(dout), ptr(lse2), ptr(seq_start), ptr(dqkv), ptr(dq_acc), ptr(D),
                                     ptr(rope_table), seq_len if rope_table is not None else 1, M, H, KV, hd, qkv.stride(0),
                                     o.stride(0), dout.stride(0), dqkv.stride(0), scale, ptr(status_word(qkv.device)),
                                     stream_ptr()), "pb_attn_bwd")

@@ -142,11 +142,11 @@ def _pair_ok(M: int, N: int) -> bool:
     return _GEMM_PAIR and M >= 512 and N >= 256
 
 
-def _gemm_epi(a, b, out, M, N, K, b_mn, epi, i0, i1, i2, aux, what):
+def _gemm_epi(a, b, out, M, N, K, b_mn, epi, i0, i1, i2, aux, what, aux2=None):
     rc = native.cuda().pb_gemm_bf16_pair_epi(ptr(a), ptr(b), ptr(out), None, M, N, K, a.stride(0), b.stride(0),
                                              out.stride(0) if out is not None else 0, 0, 0, int(b_mn), 0, 0, epi, i0, i1, i2,
-                                             ptr(aux), aux.stride(0) if aux.dim() == 2 else 0, ptr(status_word(a.device)),
-                                             stream_ptr())
+                                             ptr(aux), aux.stride(0) if aux.dim() == 2 else 0, ptr(aux2),
+                                             ptr(status_word(a.device)), stream_ptr())
     check(rc, f"pb_gemm_bf16_pair_epi[{what}](M={M},N={N},K={K})")
 
 
@@ -192,6 +192,20 @@ def gemm_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, table: torch.
     gemm(x, w, out=out)
     rope_(out, table, seq_len, n_rot_heads, head_dim)
     return out
+
+
+def gemm_rowdot(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, other: torch.Tensor, dots: torch.Tensor, group: int,
+                b_mn: bool = False) -> bool:
+    """``out = a @ op(b).T`` (bf16) and ``dots[g, m] = sum_{c in group g} out_fp32[m, c] * other[m, c]`` for column groups of
+    ``group`` columns, in one kernel (the dO . O row sums of the attention backward, taken in the epilogue of the
+    GEMM that produces dO). Returns False without touching anything when the fused kernel does not apply."""
+    M = a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if not (a.is_cuda and _pair_ok(M, N) and group == 64 and N % 64 == 0 and out.stride(-1) == 1 and other.stride(-1) == 1
+            and other.shape == out.shape and dots.is_contiguous() and dots.numel() >= (N // 64) * M):
+        return False
+    _gemm_epi(a, b, out, M, N, a.shape[1], b_mn, 4, 64, 0, 0, other, "rowdot", aux2=dots)
+    return True
 
 
 # ---------------------------------------------------------------------------------------------

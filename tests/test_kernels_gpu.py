@@ -110,6 +110,25 @@ def test_gemm_split_k_weight_gradient(M, N, K, res):
     assert _rel(acc, want) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(1024, 256, 256), (3000, 1024, 512), (4096, 1024, 1024)])
+def test_gemm_fused_rowdot_epilogue(M, N, K):
+    """dO = dh @ wo with the dO . O row sums of every 64-column head taken in the same kernel."""
+    torch.manual_seed(0)
+    dev = "cuda"
+    dh = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    wo = (torch.randn(K, N, device=dev) * K ** -0.5).bfloat16()          # [D, H*hd], used N-major (dgrad)
+    o = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    dots = torch.full(((N // 64) * M,), float("nan"), device=dev)
+    assert ops.gemm_rowdot(dh, wo, out, o, dots, 64, b_mn=True)
+    ref = dh.float() @ wo.float()
+    ref_d = (ref * o.float()).reshape(M, N // 64, 64).sum(-1).t().contiguous()      # [heads, M]
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel(out, ref) < 1e-2
+    assert _rel(dots.view(N // 64, M), ref_d) < 1e-2
+
+
 def test_gemm_persistent_many_tiles():
     torch.manual_seed(1)
     a = torch.randn(8192, 1024, device="cuda", dtype=torch.bfloat16)
