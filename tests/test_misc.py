@@ -222,3 +222,25 @@ def test_soap_optimizer_matches_adam_in_a_fixed_basis_and_converges():
     # state round trip
     sd = copy.deepcopy(opt.state_dict())
     opt.load_state_dict(sd)
+
+
+def test_convert_dl_state_positions_from_both_reference_layouts():
+    from prime_b200.cli.convert_dl_state import source_positions, transfer
+    streaming = {"_snapshot": {"_worker_snapshots": {
+        "worker_0": {"dataset_state": {"ex_iterable": {"ex_iterables": [{"ex_iterable": {"shard_idx": 4, "shard_example_idx": 10}},
+                                                                         {"ex_iterable": {"shard_idx": 1, "shard_example_idx": 0}}]}}},
+        "worker_1": {"dataset_state": {"ex_iterable": {"ex_iterables": [{"ex_iterable": {"shard_idx": 6, "shard_example_idx": 3}},
+                                                                         {"ex_iterable": {"shard_idx": 0, "shard_example_idx": 9}}]}}}}}}
+    assert source_positions(streaming) == [{"file_index": 7, "row_index": None}, {"file_index": 2, "row_index": None}]
+    parquet = {"_snapshot": {"_worker_snapshots": {"worker_0": {"dataset_state": {"dataset": {
+        "dataset_0": {"files": ["a", "b", "c"], "file_index": 2, "row_index": 40, "increment": 4, "init_row_index": 0},
+        "dataset_1": {"files": ["d"], "file_index": 0, "row_index": 8, "increment": 4, "init_row_index": 0}}}}}}}
+    new = {"loader": {"dataset": {"dataset": {"dataset_0": {"files": ["a", "b", "c"], "file_index": 0, "row_index": 1, "init_row_index": 1},
+                                              "dataset_1": {"files": ["d"], "file_index": 0, "row_index": 1, "init_row_index": 1}}},
+                      "batches_yielded": 1}, "ready_batch": None, "started": False}
+    assert transfer(parquet, new) == 2
+    d = new["loader"]["dataset"]["dataset"]
+    assert (d["dataset_0"]["file_index"], d["dataset_0"]["row_index"]) == (2, 40)
+    assert transfer(streaming, new) == 2
+    assert (d["dataset_0"]["file_index"], d["dataset_0"]["row_index"]) == (7 % 3, 1)       # next shard, from its first row
+    assert (d["dataset_1"]["file_index"], d["dataset_1"]["row_index"]) == (0, 1)
