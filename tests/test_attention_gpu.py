@@ -64,3 +64,27 @@ def test_attention_bwd_with_fused_inverse_rope():
     got = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd, rope_table=tab, seq_len=T)
     assert _rel(got, want) < 1.5e-2
     ops.check_status()
+
+
+def test_attention_long_context_gqa_packed():
+    """The 10B configuration's attention shape class: T = 8192, head size 128, 4 query heads per KV head,
+    packed documents. Dense fp32 reference on the GPU (a few heads keep its T x T scores affordable)."""
+    B, T, H, KV, hd = 1, 8192, 8, 2, 128
+    torch.manual_seed(5)
+    qkv = (torch.randn(B * T, (H + 2 * KV) * hd, device="cuda") * 0.7).bfloat16()
+    ss = A.seq_start_from_seqlens([[3000, 1, 2999, 2192]], T, "cuda")
+    o, lse2 = A.attention_fwd(qkv, ss, H, KV, hd)
+    dout = (torch.randn(B * T, H * hd, device="cuda") * 0.5).bfloat16()
+    dqkv = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd)
+    torch.cuda.synchronize()
+    ops.check_status()
+    x = qkv.float().requires_grad_(True)
+    ref = A.attention_reference(x, ss, H, KV, hd)
+    (gref,) = torch.autograd.grad(ref, x, dout.float())
+    assert _rel(o, ref) < 2e-2
+    assert _rel(dqkv, gref) < 3e-2
+    # no leakage across documents: perturbing the first document leaves the outputs of the others untouched
+    qkv2 = qkv.clone()
+    qkv2[:3000] += 1.0
+    o2, _ = A.attention_fwd(qkv2, ss, H, KV, hd)
+    assert torch.equal(o2[3000:], o[3000:])
