@@ -224,11 +224,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sfree);
             const bool need_mask = (kv0 + 127 > q0) || (kv0 < tile_last_start);
-            // row maximum over eight independent chains (a single chain of 128 dependent max
-            // instructions would cost their latency 128 times with only two warps per scheduler)
-            float mxp[8];
-#pragma unroll
-            for (int t = 0; t < 8; ++t) mxp[t] = -INFINITY;
+            // row maximum: 3-input max over four independent chains
             if (need_mask) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
@@ -236,15 +232,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                     for (int i = 0; i < 32; ++i) {
                         const int s = kv0 + 32 * q + i;
                         if (!(s <= row && s >= my_start)) v[q][i] = 0xff800000u;      // -inf
-                        mxp[i & 7] = fmaxf(mxp[i & 7], __uint_as_float(v[q][i]));
                     }
-            } else {
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mxp[i & 7] = fmaxf(mxp[i & 7], __uint_as_float(v[q][i]));
             }
-            const float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])), fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
+            float mxp[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2)
+                    mxp[(i >> 1) & 3] = max3(mxp[(i >> 1) & 3], __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
+            const float mx = fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3]));
             bool o_done = (j == 0);   // PV of the previous tile has retired (P and O may be touched)
             const bool grow = (mx != -INFINITY) && (m_used == -INFINITY || (mx - m_used) * c > 8.f);
             if (__any_sync(0xffffffffu, grow)) {
@@ -277,27 +273,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                 if (!ok) break;
                 tc_fence_after();
             }
-            // Exponentials are taken two at a time on packed bf16 pairs (ex2.approx.bf16x2): P is stored
-            // as bf16 anyway, and the packed form halves the load on the 16-per-clock special-function
-            // unit, which is what bounds this loop. The row sum adds the very values the MMA will read.
-            float rsp[8];   // eight independent partial row sums, for the same reason
-#pragma unroll
-            for (int t = 0; t < 8; ++t) rsp[t] = 0.f;
+            // P = exp2(S*c - m*c): the scale-and-shift and the row sum run on packed fp32 pairs (one f32x2
+            // instruction per two scores), the exponentials on the special-function unit (16 per clock per SM
+            // whether packed or not, so they are taken in fp32, one per score)
+            const unsigned long long cc = f32x2_pack(c, c), nm = f32x2_pack(-m_sub, -m_sub);
+            unsigned long long rs2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint32_t pw[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float x0 = __uint_as_float(v[q][2 * i]) * c - m_sub;       // masked entries are -inf -> 0
-                    const float x1 = __uint_as_float(v[q][2 * i + 1]) * c - m_sub;
-                    uint32_t e;
-                    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(pack_bf16x2(x0, x1)));
-                    pw[i] = e;
-                    rsp[i & 7] += __uint_as_float(e << 16) + __uint_as_float(e & 0xffff0000u);
+                    const unsigned long long x2 =
+                        f32x2_fma(f32x2_pack(__uint_as_float(v[q][2 * i]), __uint_as_float(v[q][2 * i + 1])), cc, nm);
+                    float x0, x1;
+                    f32x2_unpack(x2, x0, x1);
+                    const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);      // masked entries are -inf -> 0
+                    pw[i] = pack_bf16x2(e0, e1);
+                    rs2[i & 3] = f32x2_add(rs2[i & 3], f32x2_pack(e0, e1));
                 }
                 tmem_st16(tP + lane_off + 16 * q, pw);   // 32 kv columns = 16 packed words of this row
             }
-            l_run += ((rsp[0] + rsp[1]) + (rsp[2] + rsp[3])) + ((rsp[4] + rsp[5]) + (rsp[6] + rsp[7]));
+            {
+                float a0, a1;
+                f32x2_unpack(f32x2_add(f32x2_add(rs2[0], rs2[1]), f32x2_add(rs2[2], rs2[3])), a0, a1);
+                l_run += a0 + a1;
+            }
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
