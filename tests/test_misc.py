@@ -244,3 +244,25 @@ def test_convert_dl_state_positions_from_both_reference_layouts():
     assert transfer(streaming, new) == 2
     assert (d["dataset_0"]["file_index"], d["dataset_0"]["row_index"]) == (7 % 3, 1)       # next shard, from its first row
     assert (d["dataset_1"]["file_index"], d["dataset_1"]["row_index"]) == (0, 1)
+
+
+@pytest.mark.parametrize("sanitizer", ["address,undefined", "thread"])
+def test_host_library_under_sanitizers(sanitizer, tmp_path):
+    """The host quantiser and TCP ring, built with ASan+UBSan and with TSan, run their own C++ driver
+    (tests/native/host_sanitize.cpp: odd sizes, tails, a 3-rank loopback ring on threads) without a report."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "host_san")
+    src = [os.path.join(root, "tests/native/host_sanitize.cpp"), os.path.join(root, "prime_b200/csrc/host/quantize.cpp"),
+           os.path.join(root, "prime_b200/csrc/host/tcp_ring.cpp")]
+    cc = subprocess.run(["g++", "-std=c++17", "-O1", "-g", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer", *src, "-o", exe,
+                         "-lpthread"], capture_output=True, text=True)
+    if cc.returncode != 0 and "sanitize" in cc.stderr:
+        pytest.skip("sanitizer runtime not installed")
+    assert cc.returncode == 0, cc.stderr[-2000:]
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, (run.stdout + run.stderr)[-3000:]
+    assert "0 failure(s)" in run.stdout
