@@ -30,7 +30,17 @@ struct SegTable {
     long long full_off[MAX_SEGS];
     long long shard_off[MAX_SEGS];
     long long numel[MAX_SEGS];
+    // CTAs [cta_begin[s], cta_begin[s + 1]) work on segment s, in proportion to its size, so that all segments of
+    // a launch stream at once (a grid-stride pass of the whole grid over one small segment leaves most of it idle)
+    int cta_begin[MAX_SEGS + 1];
 };
+// this CTA's segment and its position among the CTAs of that segment
+__device__ __forceinline__ void my_segment(const SegTable& segs, int& s, long long& b, long long& nb) {
+    s = 0;
+    while (s + 1 < segs.n && int(blockIdx.x) >= segs.cta_begin[s + 1]) ++s;
+    b = blockIdx.x - segs.cta_begin[s];
+    nb = segs.cta_begin[s + 1] - segs.cta_begin[s];
+}
 struct PeerTable {
     int world, rank;
     void* ptr[MAX_RANKS];
@@ -100,6 +110,44 @@ __global__ void allreduce_scalars_kernel(PeerTable flag_pads, PeerTable data_pad
 template <typename G>
 __device__ __forceinline__ float ld_grad(const G* p) { return float(*p); }
 
+// Sum of `nvec` 8-element bf16 vectors over the W ranks (rank order), scaled, written as fp32; returns this
+// thread's sum of squares. UNR vectors per thread and step with every peer load issued before the first add:
+// enough bytes in flight for HBM (one rank) and for NVLink (several ranks) alike.
+template <int WMAX, int UNR>
+__device__ __forceinline__ float reduce_vectors(const PeerTable& peers, int W, long long fo, long long nvec, float scale,
+                                                float* __restrict__ dst, long long b, long long nb) {
+    float ss = 0.f;
+    const long long stride = nb * blockDim.x;
+    for (long long i0 = b * blockDim.x + threadIdx.x; i0 < nvec; i0 += UNR * stride) {
+        uint4 v[UNR][WMAX];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const long long i = i0 + u * stride;
+#pragma unroll
+            for (int r = 0; r < WMAX; ++r)
+                if (r < W && i < nvec) v[u][r] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peers.ptr[r]) + fo) + i);
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < nvec) {
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                for (int r = 0; r < WMAX; ++r)
+                    if (r < W) {
+                        const float2 a = unpack_bf16x2(v[u][r].x), b = unpack_bf16x2(v[u][r].y), c = unpack_bf16x2(v[u][r].z), d = unpack_bf16x2(v[u][r].w);
+                        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+                    }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { acc[k] *= scale; ss += acc[k] * acc[k]; }
+                reinterpret_cast<float4*>(dst)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            }
+        }
+    }
+    return ss;
+}
+
 // Reduce-scatter by pull + cast/scale + sum of squares. grid-stride over the segment elements.
 template <typename G>
 __global__ void __launch_bounds__(256) zero_reduce_grads_kernel(PeerTable peers, SegTable segs, float* __restrict__ grad_shard,
@@ -107,32 +155,19 @@ __global__ void __launch_bounds__(256) zero_reduce_grads_kernel(PeerTable peers,
     __shared__ float red[8];
     float ss = 0.f;
     const int W = peers.world;
-    for (int s = 0; s < segs.n; ++s) {
+    int s;
+    long long b, nb;
+    my_segment(segs, s, b, nb);
+    if (nb > 0) {
         const long long n = segs.numel[s];
         const long long fo = segs.full_off[s];
         float* dst = grad_shard + segs.shard_off[s];
         // vector path: 8 elements per thread per step when everything is 16-byte aligned
         const bool vec_ok = (fo % 8 == 0) && (segs.shard_off[s] % 4 == 0) && sizeof(G) == 2;
         const long long nvec = vec_ok ? n / 8 : 0;
-        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            // issue all peer loads first (W independent 16-byte loads in flight), then add in rank order
-            uint4 v[MAX_RANKS];
-#pragma unroll
-            for (int r = 0; r < MAX_RANKS; ++r)
-                if (r < W) v[r] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peers.ptr[r]) + fo) + i);
-#pragma unroll
-            for (int r = 0; r < MAX_RANKS; ++r)
-                if (r < W) {
-                    const float2 a = unpack_bf16x2(v[r].x), b = unpack_bf16x2(v[r].y), c = unpack_bf16x2(v[r].z), d = unpack_bf16x2(v[r].w);
-                    acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
-                }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) { acc[k] *= scale; ss += acc[k] * acc[k]; }
-            reinterpret_cast<float4*>(dst)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-        }
-        for (long long i = nvec * 8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        if (W <= 4) ss += reduce_vectors<4, 4>(peers, W, fo, nvec, scale, dst, b, nb);
+        else ss += reduce_vectors<MAX_RANKS, 1>(peers, W, fo, nvec, scale, dst, b, nb);
+        for (long long i = nvec * 8 + b * blockDim.x + threadIdx.x; i < n; i += nb * blockDim.x) {
             float acc = 0.f;
             for (int r = 0; r < W; ++r) acc += ld_grad(reinterpret_cast<const G*>(peers.ptr[r]) + fo + i);
             acc *= scale;
@@ -171,44 +206,60 @@ __global__ void __launch_bounds__(256) zero_adamw_gather_kernel(PeerTable params
         clip = c < 1.f ? c : 1.f;
     }
     const int W = params.world;
-    for (int s = 0; s < segs.n; ++s) {
+    int s;
+    long long b, nb;
+    my_segment(segs, s, b, nb);
+    if (nb > 0) {
         const long long n = segs.numel[s], fo = segs.full_off[s], so = segs.shard_off[s];
         const bool vec_ok = (fo % 8 == 0) && (so % 4 == 0);
         const long long nvec = vec_ok ? n / 8 : 0;
-        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-            float p[8], g[8], mm[8], vv[8];
-            *reinterpret_cast<float4*>(p) = reinterpret_cast<const float4*>(master + so)[2 * i];
-            *reinterpret_cast<float4*>(p + 4) = reinterpret_cast<const float4*>(master + so)[2 * i + 1];
-            *reinterpret_cast<float4*>(g) = reinterpret_cast<const float4*>(grad_shard + so)[2 * i];
-            *reinterpret_cast<float4*>(g + 4) = reinterpret_cast<const float4*>(grad_shard + so)[2 * i + 1];
-            *reinterpret_cast<float4*>(mm) = reinterpret_cast<const float4*>(m + so)[2 * i];
-            *reinterpret_cast<float4*>(mm + 4) = reinterpret_cast<const float4*>(m + so)[2 * i + 1];
-            *reinterpret_cast<float4*>(vv) = reinterpret_cast<const float4*>(v + so)[2 * i];
-            *reinterpret_cast<float4*>(vv + 4) = reinterpret_cast<const float4*>(v + so)[2 * i + 1];
+        // two 8-element vectors per thread and step: sixteen 16-byte streaming loads are issued before the first use
+        const long long stride = nb * blockDim.x;
+        for (long long i0 = b * blockDim.x + threadIdx.x; i0 < nvec; i0 += 2 * stride) {
+            float p[2][8], g[2][8], mm[2][8], vv[2][8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float gi = g[k] * clip;
-                p[k] *= (1.f - lr * wd);
-                mm[k] = beta1 * mm[k] + (1.f - beta1) * gi;
-                vv[k] = beta2 * vv[k] + (1.f - beta2) * gi * gi;
-                p[k] -= (lr / bc1) * (mm[k] / (sqrtf(vv[k]) / bc2 + eps));
-            }
-            reinterpret_cast<float4*>(master + so)[2 * i] = *reinterpret_cast<float4*>(p);
-            reinterpret_cast<float4*>(master + so)[2 * i + 1] = *reinterpret_cast<float4*>(p + 4);
-            reinterpret_cast<float4*>(m + so)[2 * i] = *reinterpret_cast<float4*>(mm);
-            reinterpret_cast<float4*>(m + so)[2 * i + 1] = *reinterpret_cast<float4*>(mm + 4);
-            reinterpret_cast<float4*>(v + so)[2 * i] = *reinterpret_cast<float4*>(vv);
-            reinterpret_cast<float4*>(v + so)[2 * i + 1] = *reinterpret_cast<float4*>(vv + 4);
-            uint4 o;
-            o.x = pack_bf16x2(p[0], p[1]); o.y = pack_bf16x2(p[2], p[3]); o.z = pack_bf16x2(p[4], p[5]); o.w = pack_bf16x2(p[6], p[7]);
+            for (int u = 0; u < 2; ++u) {
+                const long long i = i0 + u * stride;
+                if (i < nvec) {
 #pragma unroll
-            for (int r = 0; r < MAX_RANKS; ++r)
-                if (r < W) {
-                    const int dstr = (params.rank + r) % W;   // rotate so ranks push to different GPUs at once
-                    reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.ptr[dstr]) + fo)[i] = o;
+                    for (int h = 0; h < 2; ++h) {
+                        *reinterpret_cast<float4*>(p[u] + 4 * h) = __ldcs(reinterpret_cast<const float4*>(master + so) + 2 * i + h);
+                        *reinterpret_cast<float4*>(g[u] + 4 * h) = __ldcs(reinterpret_cast<const float4*>(grad_shard + so) + 2 * i + h);
+                        *reinterpret_cast<float4*>(mm[u] + 4 * h) = __ldcs(reinterpret_cast<const float4*>(m + so) + 2 * i + h);
+                        *reinterpret_cast<float4*>(vv[u] + 4 * h) = __ldcs(reinterpret_cast<const float4*>(v + so) + 2 * i + h);
+                    }
                 }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const long long i = i0 + u * stride;
+                if (i >= nvec) break;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float gi = g[u][k] * clip;
+                    p[u][k] *= (1.f - lr * wd);
+                    mm[u][k] = beta1 * mm[u][k] + (1.f - beta1) * gi;
+                    vv[u][k] = beta2 * vv[u][k] + (1.f - beta2) * gi * gi;
+                    p[u][k] -= (lr / bc1) * (mm[u][k] / (sqrtf(vv[u][k]) / bc2 + eps));
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    __stcs(reinterpret_cast<float4*>(master + so) + 2 * i + h, *reinterpret_cast<float4*>(p[u] + 4 * h));
+                    __stcs(reinterpret_cast<float4*>(m + so) + 2 * i + h, *reinterpret_cast<float4*>(mm[u] + 4 * h));
+                    __stcs(reinterpret_cast<float4*>(v + so) + 2 * i + h, *reinterpret_cast<float4*>(vv[u] + 4 * h));
+                }
+                uint4 o;
+                o.x = pack_bf16x2(p[u][0], p[u][1]); o.y = pack_bf16x2(p[u][2], p[u][3]);
+                o.z = pack_bf16x2(p[u][4], p[u][5]); o.w = pack_bf16x2(p[u][6], p[u][7]);
+#pragma unroll
+                for (int r = 0; r < MAX_RANKS; ++r)
+                    if (r < W) {
+                        const int dstr = (params.rank + r) % W;   // rotate so ranks push to different GPUs at once
+                        reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.ptr[dstr]) + fo)[i] = o;
+                    }
+            }
         }
-        for (long long i = nvec * 8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        for (long long i = nvec * 8 + b * blockDim.x + threadIdx.x; i < n; i += nb * blockDim.x) {
             const float gi = grad_shard[so + i] * clip;
             float pi = master[so + i] * (1.f - lr * wd);
             const float mi = beta1 * m[so + i] + (1.f - beta1) * gi;
@@ -240,10 +291,28 @@ static PeerTable make_peers(void* const* ptrs, int world, int rank) {
     for (int r = 0; r < world && r < MAX_RANKS; ++r) t.ptr[r] = ptrs[r];
     return t;
 }
-static SegTable make_segs(int n, const long long* full_off, const long long* shard_off, const long long* numel) {
+static SegTable make_segs(int n, const long long* full_off, const long long* shard_off, const long long* numel, int ctas = 0) {
     SegTable s{};
     s.n = n;
-    for (int i = 0; i < n; ++i) { s.full_off[i] = full_off[i]; s.shard_off[i] = shard_off[i]; s.numel[i] = numel[i]; }
+    long long total = 0;
+    for (int i = 0; i < n; ++i) { s.full_off[i] = full_off[i]; s.shard_off[i] = shard_off[i]; s.numel[i] = numel[i]; total += numel[i]; }
+    // CTA ranges: every non-empty segment gets at least one CTA, the rest go by size (largest remainder not needed:
+    // the last segment takes what is left)
+    int given = 0;
+    for (int i = 0; i < n; ++i) {
+        s.cta_begin[i] = given;
+        int want = 0;
+        if (numel[i] > 0 && ctas > 0) {
+            want = int((long double)numel[i] / (long double)(total > 0 ? total : 1) * ctas);
+            if (want < 1) want = 1;
+            const int nonempty_after = [&] { int c = 0; for (int j = i + 1; j < n; ++j) c += numel[j] > 0; return c; }();
+            if (given + want > ctas - nonempty_after) want = ctas - nonempty_after - given;
+            if (i == n - 1 || nonempty_after == 0) want = ctas - given;
+            if (want < 1) want = 1;
+        }
+        given += want;
+    }
+    s.cta_begin[n] = given;
     return s;
 }
 
@@ -277,7 +346,10 @@ extern "C" int pb_zero_reduce_grads(void* const* peer_grads, int world, int rank
                                     void* stream) {
     if (world > MAX_RANKS || nseg > MAX_SEGS) return -1;
     PeerTable pt = make_peers(peer_grads, world, rank);
-    SegTable sg = make_segs(nseg, full_off, shard_off, numel);
+    if (ctas < nseg) ctas = nseg;
+    SegTable sg = make_segs(nseg, full_off, shard_off, numel, ctas);
+    ctas = sg.cta_begin[nseg];
+    if (ctas <= 0) return 0;
     if (grad_fp32) zero_reduce_grads_kernel<float><<<ctas, 256, 0, ST(stream)>>>(pt, sg, grad_shard, scale, partial);
     else zero_reduce_grads_kernel<__nv_bfloat16><<<ctas, 256, 0, ST(stream)>>>(pt, sg, grad_shard, scale, partial);
     reduce_partials_kernel<<<1, 32, 0, ST(stream)>>>(partial, ctas, sumsq_out, accumulate);
@@ -291,9 +363,11 @@ extern "C" int pb_zero_adamw_gather(void* const* peer_params, int world, int ran
     if (world > MAX_RANKS || nseg > MAX_SEGS) return -1;
     const float bc1 = 1.f - powf(beta1, float(step));
     const float bc2 = sqrtf(1.f - powf(beta2, float(step)));
-    zero_adamw_gather_kernel<<<ctas, 256, 0, ST(stream)>>>(make_peers(peer_params, world, rank),
-                                                           make_segs(nseg, full_off, shard_off, numel), master, grad_shard, m, v, lr,
-                                                           beta1, beta2, eps, wd, bc1, bc2, gnorm_sq, max_norm);
+    if (ctas < nseg) ctas = nseg;
+    const SegTable sg = make_segs(nseg, full_off, shard_off, numel, ctas);
+    if (sg.cta_begin[nseg] <= 0) return 0;
+    zero_adamw_gather_kernel<<<sg.cta_begin[nseg], 256, 0, ST(stream)>>>(make_peers(peer_params, world, rank), sg, master, grad_shard, m, v,
+                                                                         lr, beta1, beta2, eps, wd, bc1, bc2, gnorm_sq, max_norm);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 
