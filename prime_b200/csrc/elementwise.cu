@@ -461,7 +461,9 @@ extern "C" int pb_cross_entropy(void* logits, const long long* labels, float* lo
                                 int ignore_index, int z_mode, float z_weight, int write_grad, void* stream) {
     if (rows <= 0) return 0;
     if (ld % 8) return -1;
-    cross_entropy_kernel<<<(unsigned)rows, 512, 0, ST(stream)>>>((__nv_bfloat16*)logits, labels, loss_rows, z_rows, inv_count,
+    // 256 threads per row: more resident CTAs per SM overlap one row's exponentials with another's loads (260 us
+    // against 296 us with 512 threads for 8192 x 32000)
+    cross_entropy_kernel<<<(unsigned)rows, 256, 0, ST(stream)>>>((__nv_bfloat16*)logits, labels, loss_rows, z_rows, inv_count,
                                                                  grad_scale, V, ld, ignore_index, z_mode, z_weight, write_grad);
     return CHECK_LAUNCH();
 }
