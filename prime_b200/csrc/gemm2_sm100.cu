@@ -345,7 +345,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // whole 128-byte rows instead of 64-byte pieces 32 rows apart; the fused SwiGLU backward also
         // fetches its inputs that way, one block ahead. fp32 outputs and residual adds use direct stores.
         const int et = threadIdx.x - 64;                           // 0..255 within the eight epilogue warps
-        const bool staged = EPI == GEMM_EPI_SWIGLU || EPI == GEMM_EPI_DSWIGLU || EPI == GEMM_EPI_ROWDOT || p.staged;
+        const bool staged = EPI == GEMM_EPI_SWIGLU || EPI == GEMM_EPI_DSWIGLU || EPI == GEMM_EPI_ROWDOT || EPI == GEMM_EPI_ADD || p.staged;
         auto epi_sync = [] { asm volatile("bar.sync 2, 256;" ::: "memory"); };
         // this thread's 64-byte piece (32 bf16 = chunks ch0..ch0+3 of 16 bytes) of row r in a staging box
         auto box_off = [&](int box, int ch) { return box * G2_BOX_BYTES + row_in_half * 128 + (((ch) ^ (row_in_half & 7)) << 4); };
@@ -361,7 +361,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 tma_load_2d(s_epi + G2_BOX_BYTES, &em.aux, bar_eload, p.epi_i0 + n0, m0);
             }
         }
-        if constexpr (EPI == GEMM_EPI_ROWDOT) {
+        if constexpr (EPI == GEMM_EPI_ROWDOT || EPI == GEMM_EPI_ADD) {
             // the two 64-column boxes of the other matrix for the first round of the first tile
             if (et == 0 && pair < p.num_items) {
                 const int m0 = (pair / p.tiles_n) * 256 + int(rank) * 128, n0 = (pair % p.tiles_n) * G2_BN;
@@ -483,7 +483,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         tma_store_commit();
                     }
                 }
-            } else if constexpr (EPI == GEMM_EPI_ROWDOT) {
+            } else if constexpr (EPI == GEMM_EPI_ROWDOT || EPI == GEMM_EPI_ADD) {
                 // two rounds of 128 columns; buffer b = boxes 2b, 2b+1 arrive holding the other matrix and leave
                 // holding C; this warp owns box `half` of the round = the 64 columns of one head of its row
 #pragma unroll 1
@@ -523,13 +523,17 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                             for (int t = 0; t < 4; ++t) {
                                 const float2 x2 = unpack_bf16x2(xw[t]);
                                 const float c0 = __uint_as_float(v[8 * q + 2 * t]), c1 = __uint_as_float(v[8 * q + 2 * t + 1]);
-                                dot += c0 * x2.x + c1 * x2.y;
-                                o[t] = pack_bf16x2(c0, c1);
+                                if constexpr (EPI == GEMM_EPI_ADD) {
+                                    o[t] = pack_bf16x2(c0 + x2.x, c1 + x2.y);
+                                } else {
+                                    dot += c0 * x2.x + c1 * x2.y;
+                                    o[t] = pack_bf16x2(c0, c1);
+                                }
                             }
                             *px = make_uint4(o[0], o[1], o[2], o[3]);
                         }
                     }
-                    if (row < p.M && cb < p.N) reinterpret_cast<float*>(p.aux2)[(long long)(cb / 64) * p.M + row] = dot;
+                    if (EPI == GEMM_EPI_ROWDOT && row < p.M && cb < p.N) reinterpret_cast<float*>(p.aux2)[(long long)(cb / 64) * p.M + row] = dot;
                     fence_proxy_async_smem();
                     epi_sync();
                     if (et == 0) {
@@ -664,6 +668,7 @@ extern "C" int pb_gemm_bf16_pair(const void* A, const void* B, void* C, const vo
 //   epi 2 (RoPE)    : epi_i0 = T, epi_i1 = number of leading columns to rotate, epi_i2 = head size, aux = fp32 table
 //   epi 3 (dSwiGLU) : N = F = epi_i0, aux = h13 (read gate | up, written d gate | d up), C unused
 //   epi 4 (row dot) : aux = bf16 [M, N] with pitch ldaux, epi_i0 = 64 columns per group, aux2 = fp32 [N / 64, M]
+//   epi 5 (add)     : aux = bf16 [M, N] addend with pitch ldaux (may be C)
 extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
                                      long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_fp32, int max_ctas,
                                      int epi, int epi_i0, int epi_i1, int epi_i2, void* aux, long long ldaux, void* aux2,
@@ -676,7 +681,8 @@ extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, cons
         if (epi == GEMM_EPI_ROPE && (a_mn || b_mn || epi_i0 <= 0 || epi_i2 % 64 || epi_i1 % 64 || epi_i1 > N)) return -4;
         if (epi == GEMM_EPI_DSWIGLU && (a_mn || !b_mn || N != epi_i0 || epi_i0 % 64 || ldaux % 8)) return -4;
         if (epi == GEMM_EPI_ROWDOT && (a_mn || epi_i0 != 64 || ldaux % 8 || !aux2)) return -4;
-        if (epi < 0 || epi > GEMM_EPI_ROWDOT) return -4;
+        if (epi == GEMM_EPI_ADD && (ldaux % 8)) return -4;
+        if (epi < 0 || epi > GEMM_EPI_ADD) return -4;
     }
     if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
     const int vec = out_fp32 ? 4 : 8;
@@ -701,7 +707,7 @@ extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, cons
     }
     if (epi == GEMM_EPI_SWIGLU) rc = make_tmap_bf16_2d(&em.aux, aux, epi_i0, M, ldaux, 64, 128);
     if (epi == GEMM_EPI_DSWIGLU) rc = make_tmap_bf16_2d(&em.aux, aux, 2 * uint64_t(epi_i0), M, ldaux, 64, 128);
-    if (epi == GEMM_EPI_ROWDOT) rc = make_tmap_bf16_2d(&em.aux, aux, N, M, ldaux, 64, 128);
+    if (epi == GEMM_EPI_ROWDOT || epi == GEMM_EPI_ADD) rc = make_tmap_bf16_2d(&em.aux, aux, N, M, ldaux, 64, 128);
     if (rc) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const GatherParams ng{};
@@ -710,6 +716,12 @@ extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, cons
     if (epi == GEMM_EPI_DSWIGLU) return launch_gemm_pair<false, true, false, GEMM_EPI_DSWIGLU>(tmA, tmB, p, max_ctas, st, ng, em);
     if (epi == GEMM_EPI_ROWDOT && b_mn) return launch_gemm_pair<false, true, false, GEMM_EPI_ROWDOT>(tmA, tmB, p, max_ctas, st, ng, em);
     if (epi == GEMM_EPI_ROWDOT) return launch_gemm_pair<false, false, false, GEMM_EPI_ROWDOT>(tmA, tmB, p, max_ctas, st, ng, em);
+    if (epi == GEMM_EPI_ADD) {
+        if (!a_mn && !b_mn) return launch_gemm_pair<false, false, false, GEMM_EPI_ADD>(tmA, tmB, p, max_ctas, st, ng, em);
+        if (!a_mn && b_mn)  return launch_gemm_pair<false, true, false, GEMM_EPI_ADD>(tmA, tmB, p, max_ctas, st, ng, em);
+        if (a_mn && !b_mn)  return launch_gemm_pair<true, false, false, GEMM_EPI_ADD>(tmA, tmB, p, max_ctas, st, ng, em);
+        return launch_gemm_pair<true, true, false, GEMM_EPI_ADD>(tmA, tmB, p, max_ctas, st, ng, em);
+    }
     if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, p, max_ctas, st, ng, em);
     if (!a_mn && b_mn)  return launch_gemm_pair<false, true>(tmA, tmB, p, max_ctas, st, ng, em);
     if (a_mn && !b_mn)  return launch_gemm_pair<true, false>(tmA, tmB, p, max_ctas, st, ng, em);

@@ -41,7 +41,9 @@ struct GemmParams {
 //  ROWDOT : besides the plain bf16 store of C, aux2[(col / epi_i0) * M + row] = sum over the epi_i0 (= 64) columns of
 //           one head of C[row, col] * aux[row, col] (fp32 accumulator values times a bf16 matrix of C's shape):
 //           the dO . O row sums that the attention backward needs, taken where dO is produced.
-constexpr int GEMM_EPI_NONE = 0, GEMM_EPI_SWIGLU = 1, GEMM_EPI_ROPE = 2, GEMM_EPI_DSWIGLU = 3, GEMM_EPI_ROWDOT = 4;
+//  ADD    : C = product + aux (bf16, same shape; aux may be C itself): the residual / accumulate form of the staged
+//           epilogue; the addend tiles arrive by TMA one round ahead.
+constexpr int GEMM_EPI_NONE = 0, GEMM_EPI_SWIGLU = 1, GEMM_EPI_ROPE = 2, GEMM_EPI_DSWIGLU = 3, GEMM_EPI_ROWDOT = 4, GEMM_EPI_ADD = 5;
 
 __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&f)[32]) {
 #pragma unroll

@@ -92,6 +92,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, resi
                                                 int(out.dtype == torch.float32), stream_ptr())
             check(rc, "pb_splitk_reduce")
             return out
+        if (residual is not None and out.dtype == torch.bfloat16 and residual.stride(0) % 8 == 0 and residual.data_ptr() % 16 == 0
+                and max_ctas == 0):
+            # bf16 residual / accumulate: the addend tiles come in by TMA and the sum leaves by TMA (staged epilogue)
+            _gemm_epi(a, b, out, M, N, K, b_mn, 5, 0, 0, 0, residual, "add", a_mn=a_mn)
+            return out
         rc = native.cuda().pb_gemm_bf16_pair(ptr(a), ptr(b), ptr(out), ptr(residual), M, N, K, a.stride(0), b.stride(0),
                                              out.stride(0), ldr, int(a_mn), int(b_mn), int(out.dtype == torch.float32), max_ctas,
                                              ptr(status_word(a.device)), stream_ptr())
@@ -142,9 +147,9 @@ def _pair_ok(M: int, N: int) -> bool:
     return _GEMM_PAIR and M >= 512 and N >= 256
 
 
-def _gemm_epi(a, b, out, M, N, K, b_mn, epi, i0, i1, i2, aux, what, aux2=None):
+def _gemm_epi(a, b, out, M, N, K, b_mn, epi, i0, i1, i2, aux, what, aux2=None, a_mn=False):
     rc = native.cuda().pb_gemm_bf16_pair_epi(ptr(a), ptr(b), ptr(out), None, M, N, K, a.stride(0), b.stride(0),
-                                             out.stride(0) if out is not None else 0, 0, 0, int(b_mn), 0, 0, epi, i0, i1, i2,
+                                             out.stride(0) if out is not None else 0, 0, int(a_mn), int(b_mn), 0, 0, epi, i0, i1, i2,
                                              ptr(aux), aux.stride(0) if aux.dim() == 2 else 0, ptr(aux2),
                                              ptr(status_word(a.device)), stream_ptr())
     check(rc, f"pb_gemm_bf16_pair_epi[{what}](M={M},N={N},K={K})")
