@@ -22,7 +22,7 @@
 
 namespace pb {
 
-constexpr int MAX_SEGS = 16;
+constexpr int MAX_SEGS = 128;   // one launch can cover every parameter of a model with up to ~14 blocks; tables are kernel arguments
 constexpr int MAX_RANKS = 16;
 
 struct SegTable {

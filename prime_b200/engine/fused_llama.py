@@ -51,16 +51,25 @@ native.register_cuda_sigs({
 
 
 class _SegArrays:
-    """ctypes arrays describing the segments of one group for one rank."""
+    """ctypes arrays describing the segments of one group (or of all groups) for one rank. Neighbouring
+    segments that are contiguous both in the full buffer and in the shard buffer are merged (with one rank
+    the whole model is a single segment)."""
 
     def __init__(self, segs):
-        segs = [s for s in segs if s.numel > 0]
-        self.n = len(segs)
+        runs: list[list[int]] = []
+        for s in segs:
+            if s.numel <= 0:
+                continue
+            if runs and runs[-1][0] + runs[-1][2] == s.full_offset and runs[-1][1] + runs[-1][2] == s.shard_offset:
+                runs[-1][2] += s.numel
+            else:
+                runs.append([s.full_offset, s.shard_offset, s.numel])
+        self.n = len(runs)
         arr = C.c_longlong * max(self.n, 1)
-        self.full = arr(*[s.full_offset for s in segs])
-        self.shard = arr(*[s.shard_offset for s in segs])
-        self.numel = arr(*[s.numel for s in segs])
-        self.total = sum(s.numel for s in segs)
+        self.full = arr(*[r[0] for r in runs])
+        self.shard = arr(*[r[1] for r in runs])
+        self.numel = arr(*[r[2] for r in runs])
+        self.total = sum(r[2] for r in runs)
 
 
 class LocalComm:
@@ -86,7 +95,7 @@ class FusedLlama:
 
     def __init__(self, args: ModelArgs, device: torch.device | str = "cuda", comm=None, grad_dtype=torch.bfloat16,
                  ac_ckpt: bool | int = False, ce_chunk_tokens: int = 32768, z_mode: int = K.Z_NONE, z_weight: float = 0.0,
-                 comm_ctas: int = 148):
+                 comm_ctas: int = 37):
         self.args = args
         self.device = torch.device(device)
         self.comm = comm if comm is not None else LocalComm()
@@ -112,6 +121,9 @@ class FusedLlama:
         self._segs = [_SegArrays(lay.group_segments(self.rank, g)) for g in range(len(lay.groups))]
         max_segs = native.cuda().pb_zero_max_segs() if dev.type == "cuda" else 16
         assert all(s.n <= max_segs for s in self._segs)
+        # all groups in one table: the reduce and the AdamW + push run as one launch each when it fits
+        allsegs = _SegArrays([s for g in range(len(lay.groups)) for s in lay.group_segments(self.rank, g)])
+        self._segs_step = [allsegs] if allsegs.n <= max_segs else self._segs
         self._partials = torch.zeros(4096, dtype=torch.float32, device=dev)
         self._norm_local = torch.zeros(8, dtype=torch.float32, device=dev)
         self._norm_global = torch.zeros(8, dtype=torch.float32, device=dev)
@@ -361,7 +373,7 @@ class FusedLlama:
         lib = native.cuda()
         W = self.world
         self.comm.barrier()                                   # every rank finished writing its grads
-        for g, sa in enumerate(self._segs):
+        for g, sa in enumerate(self._segs_step):
             if sa.n == 0:
                 continue
             check(lib.pb_zero_reduce_grads(self._peer_grads, W, self.rank, int(self.grad_dtype == torch.float32), sa.n, sa.full,
@@ -369,7 +381,7 @@ class FusedLlama:
                                            ptr(self._norm_local), int(g > 0), min(self.comm_ctas * 4, 1024), stream_ptr()),
                   "pb_zero_reduce_grads")
         self.comm.allreduce_scalars(self._norm_local, self._norm_global, 1)   # also orders: all ranks done reading grads
-        for g, sa in enumerate(self._segs):
+        for g, sa in enumerate(self._segs_step):
             if sa.n == 0:
                 continue
             check(lib.pb_zero_adamw_gather(self._peer_params, W, self.rank, sa.n, sa.full, sa.shard, sa.numel, ptr(self.master),

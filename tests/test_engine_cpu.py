@@ -108,3 +108,23 @@ def test_z_loss_modes_match_autograd():
         assert abs((out["loss"] + out["z_loss"]).item() - ref.item()) < 1e-4
         for name, p in model.named_parameters():
             assert (eng.g[name] - p.grad).norm() / (p.grad.norm() + 1e-12) < 1e-4, name
+
+
+def test_segment_tables_merge_contiguous_runs():
+    """With one rank neighbouring parameters are contiguous in both the full and the shard buffer and collapse
+    into few runs; with two ranks every parameter keeps its own row-shard segment."""
+    from prime_b200.engine.fused_llama import _SegArrays
+    from prime_b200.engine.layout import llama_layout
+    args = ModelArgs(dim=64, n_layers=2, n_heads=4, ffn_hidden=128, vocab_size=96, max_seq_len=32)
+    for world in (1, 2):
+        lay = llama_layout(args, world)
+        segs = [s for g in range(len(lay.groups)) for s in lay.group_segments(0, g)]
+        sa = _SegArrays(segs)
+        assert sa.total == sum(s.numel for s in segs)
+        covered = sorted((sa.full[i], sa.numel[i]) for i in range(sa.n))
+        for (o0, n0), (o1, _) in zip(covered, covered[1:]):
+            assert o0 + n0 <= o1
+        if world == 1:
+            assert sa.n < len([s for s in segs if s.numel > 0])
+        else:
+            assert sa.n <= len(segs)
