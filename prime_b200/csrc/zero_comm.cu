@@ -296,21 +296,22 @@ static SegTable make_segs(int n, const long long* full_off, const long long* sha
     s.n = n;
     long long total = 0;
     for (int i = 0; i < n; ++i) { s.full_off[i] = full_off[i]; s.shard_off[i] = shard_off[i]; s.numel[i] = numel[i]; total += numel[i]; }
-    // CTA ranges: every non-empty segment gets at least one CTA, the rest go by size (largest remainder not needed:
-    // the last segment takes what is left)
-    int given = 0;
+    // CTA ranges: segment i ends at the rounded share of the element prefix, every non-empty segment gets at
+    // least one CTA and leaves one for each non-empty segment after it; the last one ends at `ctas`
+    int given = 0, nonempty_after = 0;
+    for (int i = 0; i < n; ++i) nonempty_after += numel[i] > 0;
+    long long prefix = 0;
     for (int i = 0; i < n; ++i) {
         s.cta_begin[i] = given;
-        int want = 0;
         if (numel[i] > 0 && ctas > 0) {
-            want = int((long double)numel[i] / (long double)(total > 0 ? total : 1) * ctas);
-            if (want < 1) want = 1;
-            const int nonempty_after = [&] { int c = 0; for (int j = i + 1; j < n; ++j) c += numel[j] > 0; return c; }();
-            if (given + want > ctas - nonempty_after) want = ctas - nonempty_after - given;
-            if (i == n - 1 || nonempty_after == 0) want = ctas - given;
-            if (want < 1) want = 1;
+            --nonempty_after;
+            prefix += numel[i];
+            int end = int((long double)prefix / (long double)total * ctas + 0.5L);
+            if (end > ctas - nonempty_after) end = ctas - nonempty_after;
+            if (nonempty_after == 0) end = ctas;
+            if (end < given + 1) end = given + 1;
+            given = end;
         }
-        given += want;
     }
     s.cta_begin[n] = given;
     return s;

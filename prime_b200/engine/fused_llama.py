@@ -378,7 +378,7 @@ class FusedLlama:
                 continue
             check(lib.pb_zero_reduce_grads(self._peer_grads, W, self.rank, int(self.grad_dtype == torch.float32), sa.n, sa.full,
                                            sa.shard, sa.numel, ptr(self.grad_shard), 1.0 / W, ptr(self._partials),
-                                           ptr(self._norm_local), int(g > 0), min(self.comm_ctas * 4, 1024), stream_ptr()),
+                                           ptr(self._norm_local), int(g > 0), self._opt_ctas(sa), stream_ptr()),
                   "pb_zero_reduce_grads")
         self.comm.allreduce_scalars(self._norm_local, self._norm_global, 1)   # also orders: all ranks done reading grads
         for g, sa in enumerate(self._segs_step):
@@ -387,10 +387,19 @@ class FusedLlama:
             check(lib.pb_zero_adamw_gather(self._peer_params, W, self.rank, sa.n, sa.full, sa.shard, sa.numel, ptr(self.master),
                                            ptr(self.grad_shard), ptr(self.exp_avg), ptr(self.exp_avg_sq), lr, betas[0], betas[1],
                                            eps, weight_decay, self.opt_step, ptr(self._norm_global), max_norm,
-                                           min(self.comm_ctas * 4, 1024), stream_ptr()), "pb_zero_adamw_gather")
+                                           self._opt_ctas(sa), stream_ptr()), "pb_zero_adamw_gather")
         self.comm.barrier()                                   # every rank's replica is complete
         self._accum = False
         return self._norm_global[0].sqrt()
+
+    def _opt_ctas(self, sa) -> int:
+        """Grid of the reduce and AdamW launches. One merged segment streams best from a grid of one CTA per SM
+        slot; a table of many segments (sharded runs) needs enough CTAs for the per-segment split to follow the
+        segment sizes: one CTA per 32k elements, within the size of the partial-sum scratch."""
+        base = min(self.comm_ctas * 4, 1024)
+        if sa.n <= 1:
+            return base
+        return int(max(base, sa.n, min(sa.total // 32768, self._partials.numel())))
 
     def _optimizer_step_cpu(self, lr, betas, eps, weight_decay, max_norm) -> torch.Tensor:
         """Single-rank CPU twin of the update (same math through the CPU branches of the ops)."""
