@@ -324,6 +324,14 @@ using namespace pb;
 
 extern "C" int pb_zero_max_segs() { return MAX_SEGS; }
 extern "C" int pb_zero_max_ranks() { return MAX_RANKS; }
+// Host-only: the CTA ranges that a launch over these segments would use (cta_begin[0..nseg]); returns the grid size.
+extern "C" int pb_zero_cta_ranges(int nseg, const long long* numel, int ctas, int* cta_begin) {
+    if (nseg > MAX_SEGS || nseg < 0) return -1;
+    if (ctas < nseg) ctas = nseg;
+    const SegTable sg = make_segs(nseg, numel, numel, numel, ctas);
+    for (int i = 0; i <= nseg; ++i) cta_begin[i] = sg.cta_begin[i];
+    return sg.cta_begin[nseg];
+}
 
 extern "C" int pb_peer_barrier(void* const* pad_ptrs, int world, int rank, int slot, int epoch, int* status, void* stream) {
     if (world > MAX_RANKS) return -1;

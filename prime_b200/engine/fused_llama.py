@@ -36,6 +36,7 @@ from .layout import ParamLayout, llama_layout
 
 native.register_cuda_sigs({
     "pb_zero_max_segs": [],
+    "pb_zero_cta_ranges": [native.i32, native.vp, native.i32, native.vp],
     "pb_zero_max_ranks": [],
     "pb_peer_barrier": [native.vp, native.i32, native.i32, native.i32, native.i32, native.vp, native.vp],
     "pb_allreduce_scalars": [native.vp, native.vp, native.i32, native.i32, native.i32, native.i32, native.vp, native.vp,

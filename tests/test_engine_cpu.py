@@ -128,3 +128,36 @@ def test_segment_tables_merge_contiguous_runs():
             assert sa.n < len([s for s in segs if s.numel > 0])
         else:
             assert sa.n <= len(segs)
+
+
+def test_optimizer_cta_ranges_cover_every_segment():
+    """The reduce / AdamW launches give each non-empty segment its own CTA range: a segment without one would
+    silently keep stale gradients. Ranges are monotone, end at the grid size and follow the segment sizes."""
+    import ctypes as C
+
+    from prime_b200 import native
+    try:
+        lib = native.cuda()
+    except native.NativeError:
+        pytest.skip("CUDA library not built")
+    gen = torch.Generator().manual_seed(0)
+    cases = [[5], [1, 1, 1], [0, 7, 0, 9, 0], [1 << 24, 512, 1 << 21, 0, 3, 1 << 24],
+             torch.randint(1, 1 << 22, (111,), generator=gen).tolist(), [1] * 128]
+    for numel in cases:
+        n = len(numel)
+        arr = (C.c_longlong * n)(*numel)
+        for ctas in (1, n, 148, 640, 4096):
+            out = (C.c_int * (n + 1))()
+            grid = lib.pb_zero_cta_ranges(n, arr, ctas, out)
+            begins = list(out)
+            nonempty = sum(1 for x in numel if x > 0)
+            assert grid == begins[-1] and grid >= nonempty
+            if nonempty:
+                assert grid == max(ctas, n)
+            total = sum(numel)
+            for i, x in enumerate(numel):
+                width = begins[i + 1] - begins[i]
+                assert width >= (1 if x > 0 else 0) and (x > 0 or width == 0)
+                share = x / total * grid if total else 0.0
+                if share >= 4.0:                # large segments get about their share of the grid
+                    assert 0.5 * share <= width <= 1.5 * share + 1
