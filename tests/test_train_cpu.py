@@ -25,7 +25,21 @@ def _local_env(rank, world, port):
             "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)}
 
 
+_PORT_TROUBLE = ("Address already in use", "EADDRINUSE", "Connection refused", "Connection reset")
+
+
 def _run_job(tmp_path, name, n_workers, n_local, argv, timeout=420):
+    """Run one training job as child processes; a job that died because one of its freshly picked ports was taken by
+    another process in the meantime is started once more on new ports."""
+    try:
+        return _run_job_once(tmp_path, name, n_workers, n_local, argv, timeout)
+    except AssertionError as e:
+        if not any(t in str(e) for t in _PORT_TROUBLE):
+            raise
+    return _run_job_once(tmp_path, name + "_again", n_workers, n_local, argv, timeout)
+
+
+def _run_job_once(tmp_path, name, n_workers, n_local, argv, timeout):
     ports = get_random_available_port_list(2 + n_workers)
     procs, logs = [], []
     for w in range(n_workers):
@@ -47,7 +61,11 @@ def _run_job(tmp_path, name, n_workers, n_local, argv, timeout=420):
             for q in procs:
                 q.kill()
             raise AssertionError(f"timeout; log tail:\n{log.read_text()[-3000:]}")
-        assert rc == 0, f"{log}:\n{log.read_text()[-3000:]}"
+        if rc != 0:
+            for q in procs:
+                if q.poll() is None:
+                    q.kill()
+            raise AssertionError(f"{log}:\n{log.read_text()[-3000:]}")
     out = []
     for w in range(n_workers):
         with open(tmp_path / f"{name}_w{w}.pkl", "rb") as f:
