@@ -14,6 +14,7 @@ loaded there without recompiling.
 from __future__ import annotations
 
 import concurrent.futures as cf
+import fcntl
 import hashlib
 import os
 import shutil
@@ -58,18 +59,32 @@ def _build_lib(name: str, sources: list[Path], headers: list[Path], compiler: st
     lib = OUT / name
     stamp = OUT / (name + ".hash")
     want = _hash(sources + headers, flags + link_flags)
-    if not force and lib.exists() and stamp.exists() and stamp.read_text().strip() == want:
+    def fresh() -> bool:
+        return lib.exists() and stamp.exists() and stamp.read_text().strip() == want
+
+    if not force and fresh():
         return lib
-    objdir = OUT / ("obj_" + name.replace(".", "_"))
-    objdir.mkdir(exist_ok=True)
-    objs = [objdir / (s.stem + ".o") for s in sources]
-    with cf.ThreadPoolExecutor(max_workers=min(8, len(sources) or 1)) as ex:
-        futs = [ex.submit(_run, [compiler, *flags, f"-I{CSRC}", "-c", str(s), "-o", str(o)])
-                for s, o in zip(sources, objs)]
-        for f in futs:
-            f.result()
-    _run([compiler, "-shared", *[a for a in flags if a not in ("-c",)], *map(str, objs), "-o", str(lib), *link_flags])
-    stamp.write_text(want)
+    # several ranks of one launcher may get here at once on a new checkout: one of them builds, the others wait for
+    # the lock and find the result; the library appears under its name only when it is complete
+    with open(OUT / (name + ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and fresh():
+                return lib
+            objdir = OUT / ("obj_" + name.replace(".", "_"))
+            objdir.mkdir(exist_ok=True)
+            objs = [objdir / (s.stem + ".o") for s in sources]
+            with cf.ThreadPoolExecutor(max_workers=min(8, len(sources) or 1)) as ex:
+                futs = [ex.submit(_run, [compiler, *flags, f"-I{CSRC}", "-c", str(s), "-o", str(o)])
+                        for s, o in zip(sources, objs)]
+                for f in futs:
+                    f.result()
+            tmp = OUT / (name + f".tmp{os.getpid()}")
+            _run([compiler, "-shared", *[a for a in flags if a not in ("-c",)], *map(str, objs), "-o", str(tmp), *link_flags])
+            os.replace(tmp, lib)
+            stamp.write_text(want)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return lib
 
 

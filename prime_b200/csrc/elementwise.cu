@@ -409,9 +409,10 @@ extern "C" int pb_rmsnorm_bwd(const void* x, const void* w, const float* rstd, c
     const int ctas = pb_rmsnorm_bwd_ctas();
     auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w; auto DY = (const __nv_bfloat16*)dy;
     auto DR = (const __nv_bfloat16*)dres; auto DX = (__nv_bfloat16*)dx;
-#define RB(NCH) case NCH: rmsnorm_bwd_kernel<NCH><<<ctas, 256, 0, ST(stream)>>>(X, W, rstd, DY, DR, DX, dw_partial, M); break;
+    // rows wider than 1024 are shared by two or four warps (at most four 256-column chunks per warp)
+#define RB(NCH, WPR) case NCH: rmsnorm_bwd_kernel<NCH, WPR><<<ctas, 256, 0, ST(stream)>>>(X, W, rstd, DY, DR, DX, dw_partial, M); break;
     switch (N / 256) {
-        RB(1) RB(2) RB(3) RB(4) RB(6) RB(8) RB(12) RB(16)
+        RB(1, 1) RB(2, 1) RB(3, 1) RB(4, 1) RB(6, 2) RB(8, 2) RB(12, 4) RB(16, 4)
         default: return -1;
     }
 #undef RB

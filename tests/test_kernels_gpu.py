@@ -139,7 +139,10 @@ def test_gemm_persistent_many_tiles():
     ops.check_status()
 
 
-@pytest.mark.parametrize("M,N", [(1000, 1024), (64, 256), (300, 4096)])
+# widths with one (<= 1024), two (1536, 2048) and four (3072, 4096) warps per row in the backward; row counts that
+# leave some of a CTA's row slots empty in the last iteration
+@pytest.mark.parametrize("M,N", [(1000, 1024), (64, 256), (300, 4096), (1201, 768), (3, 512), (2501, 2048), (1999, 1536),
+                                 (4099, 3072), (9001, 4096)])
 def test_rmsnorm(M, N):
     torch.manual_seed(0)
     x = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
