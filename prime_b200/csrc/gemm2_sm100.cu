@@ -19,6 +19,7 @@
 // Every wait is bounded (status word + abort flag), both CTAs always reach the final cluster barrier.
 #include "gemm_common.cuh"
 #include <cooperative_groups.h>
+#include <cstdlib>
 
 namespace pb {
 
@@ -213,13 +214,14 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int item = pair; item < p.num_items && ok; item += n_pairs) {
             const int tile = item % p.num_tiles, slice = item / p.num_tiles;
             const int kb0 = slice * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
-            const int m0 = (tile / p.tiles_n) * 256 + int(rank) * 128;     // my half of the A rows
+            int tm, tn;
+            gemm_tile_mn(p, tile, tm, tn);
+            const int m0 = tm * 256 + int(rank) * 128;     // my half of the A rows
             // my half of the B rows; with the SwiGLU epilogue the halves are the gate rows and the matching up rows
-            const int n0 = EPI == GEMM_EPI_SWIGLU ? (tile % p.tiles_n) * 128 + int(rank) * p.epi_i0
-                                                    : (tile % p.tiles_n) * G2_BN + int(rank) * 128;
+            const int n0 = EPI == GEMM_EPI_SWIGLU ? tn * 128 + int(rank) * p.epi_i0 : tn * G2_BN + int(rank) * 128;
             if constexpr (GATHER) {
                 // wait until every row of this n-block has landed in the local B buffer
-                const int* ctr = g.counters + (tile % p.tiles_n);
+                const int* ctr = g.counters + tn;
                 const uint64_t t0 = globaltimer_ns();
                 while (ok && ld_acquire_gpu(ctr) < g.target) {
                     if (*abort_flag) ok = false;
@@ -355,7 +357,9 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         if constexpr (EPI == GEMM_EPI_DSWIGLU) {
             // gate | up of the first block of the first tile
             if (et == 0 && pair < p.num_items) {
-                const int m0 = (pair / p.tiles_n) * 256 + int(rank) * 128, n0 = (pair % p.tiles_n) * G2_BN;
+                int tm, tn;
+                gemm_tile_mn(p, pair, tm, tn);
+                const int m0 = tm * 256 + int(rank) * 128, n0 = tn * G2_BN;
                 mbar_expect_tx(bar_eload, 2 * G2_BOX_BYTES);
                 tma_load_2d(s_epi, &em.aux, bar_eload, n0, m0);
                 tma_load_2d(s_epi + G2_BOX_BYTES, &em.aux, bar_eload, p.epi_i0 + n0, m0);
@@ -364,7 +368,9 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         if constexpr (EPI == GEMM_EPI_ROWDOT || EPI == GEMM_EPI_ADD) {
             // the two 64-column boxes of the other matrix for the first round of the first tile
             if (et == 0 && pair < p.num_items) {
-                const int m0 = (pair / p.tiles_n) * 256 + int(rank) * 128, n0 = (pair % p.tiles_n) * G2_BN;
+                int tm, tn;
+                gemm_tile_mn(p, pair, tm, tn);
+                const int m0 = tm * 256 + int(rank) * 128, n0 = tn * G2_BN;
                 mbar_expect_tx(bar_eload, 2 * G2_BOX_BYTES);
                 tma_load_2d(s_epi, &em.aux, bar_eload, n0, m0);
                 tma_load_2d(s_epi + G2_BOX_BYTES, &em.aux, bar_eload, n0 + 64, m0);
@@ -374,8 +380,10 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const int tile = item % p.num_tiles, slice = item / p.num_tiles;
             const int acc = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
-            const int m0 = (tile / p.tiles_n) * 256 + int(rank) * 128;
-            const int n0 = (tile % p.tiles_n) * G2_BN;
+            int tm, tn;
+            gemm_tile_mn(p, tile, tm, tn);
+            const int m0 = tm * 256 + int(rank) * 128;
+            const int n0 = tn * G2_BN;
             ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -390,7 +398,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
             if constexpr (EPI == GEMM_EPI_SWIGLU) {
                 // two rounds of 64 features: boxes 0, 1, 2 = gate, up, act; this warp does 32 of the 64 columns
                 const int F = p.epi_i0;
-                const int j0 = (tile % p.tiles_n) * 128;
+                const int j0 = tn * 128;
 #pragma unroll 1
                 for (int rnd = 0; rnd < 2; ++rnd) {
                     uint32_t vg[32], vu[32];
@@ -437,7 +445,9 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         int nt = tile, nr = rnd + 1;
                         if (nr == 4) { nr = 0; nt += n_pairs; }
                         if (nt < p.num_tiles) {
-                            const int nm0 = (nt / p.tiles_n) * 256 + int(rank) * 128, nn0 = (nt % p.tiles_n) * G2_BN + nr * 64;
+                            int ntm, ntn;
+                            gemm_tile_mn(p, nt, ntm, ntn);
+                            const int nm0 = ntm * 256 + int(rank) * 128, nn0 = ntn * G2_BN + nr * 64;
                             tma_store_wait_read<0>();      // the stores that last used that buffer have read it
                             if (nn0 < p.N) {
                                 mbar_expect_tx(bar_eload + 8 * (buf ^ 1), 2 * G2_BOX_BYTES);
@@ -496,7 +506,9 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         int nt = tile, nr = rnd + 1;
                         if (nr == 2) { nr = 0; nt += n_pairs; }
                         if (nt < p.num_tiles) {
-                            const int nm0 = (nt / p.tiles_n) * 256 + int(rank) * 128, nn0 = (nt % p.tiles_n) * G2_BN + nr * 128;
+                            int ntm, ntn;
+                            gemm_tile_mn(p, nt, ntm, ntn);
+                            const int nm0 = ntm * 256 + int(rank) * 128, nn0 = ntn * G2_BN + nr * 128;
                             tma_store_wait_read<0>();      // the stores that last used that buffer have read it
                             mbar_expect_tx(bar_eload + 8 * (buf ^ 1), 2 * G2_BOX_BYTES);   // columns past N arrive as zeros
                             tma_load_2d(s_epi + (2 * (buf ^ 1)) * G2_BOX_BYTES, &em.aux, bar_eload + 8 * (buf ^ 1), nn0, nm0);
@@ -622,6 +634,17 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
 }
 
+// Rows of tiles per band of the tile numbering (gemm_tile_mn). Row-major numbering reads A once and B once per wave of
+// CTA pairs, which is free while B stays in L2; a B operand that does not fit there (48 MB and more: the 10B model's
+// w13 and head, the 150M model's head) would be streamed from HBM tiles_m / (rows per wave) times, so such products
+// use bands of 16 rows: [8192 x 128256 x 4096] 8.22 -> 5.81 ms, [8192 x 28672 x 4096] 1.61 -> 1.25 ms, while products
+// with a small B lose 1-2 % to banding and keep the row-major order. PRIME_B200_GEMM_GROUP_M overrides (measurements).
+static int tile_band_rows(int tiles_m, int tiles_n, long long b_bytes) {
+    static const int forced = [] { const char* e = getenv("PRIME_B200_GEMM_GROUP_M"); return e ? atoi(e) : 0; }();
+    if (forced > 0) return forced;
+    return (b_bytes >= (48ll << 20) && tiles_n > 8 && tiles_m >= 8) ? 16 : 1;
+}
+
 template <bool A_MN, bool B_MN, bool GATHER = false, int EPI = GEMM_EPI_NONE>
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t st,
                             const GatherParams& g = GatherParams{}, const EpiMaps& em = EpiMaps{}) {
@@ -634,6 +657,8 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
     const int tiles_m = (p.M + 255) / 256;
     p.tiles_n = EPI == GEMM_EPI_SWIGLU ? p.epi_i0 / 128 : (p.N + G2_BN - 1) / G2_BN;
     p.num_tiles = tiles_m * p.tiles_n;
+    p.tiles_m = tiles_m;
+    p.group_m = GATHER ? 1 : tile_band_rows(tiles_m, p.tiles_n, 2ll * p.N * p.K);
     if (p.num_items <= 0) {   // no split-K requested
         p.num_items = p.num_tiles;
         p.kb_per_split = (p.K + BK - 1) / BK;

@@ -17,6 +17,8 @@ struct GemmParams {
     int out_fp32;
     int* status;
     int num_tiles, tiles_n;
+    // CTA-pair kernel: tiles are numbered in bands of group_m tile rows (see gemm_tile_mn); tiles_m = rows of tiles
+    int tiles_m, group_m;
     // split-K: work item w = slice * num_tiles + tile; slice s covers k-blocks [s * kb_per_split, ...) and
     // stores its fp32 partial tile at C + s * split_stride elements (plain direct-store epilogue only)
     int num_items, kb_per_split;
@@ -28,6 +30,25 @@ struct GemmParams {
     long long ldaux;
     void* aux2;
 };
+
+// Output tile number -> tile row and tile column. Tiles are numbered in bands of group_m tile rows, down the rows of
+// a band first, so that the tiles in flight at one time (one per CTA pair, consecutive numbers) cover a near-square
+// block of the output and share their operand row blocks through L2: a band of 8 rows lets 74 pairs touch 8 + 10
+// operand blocks per k-step instead of 1 + 74. group_m <= 1: plain row-major numbering.
+__device__ __forceinline__ void gemm_tile_mn(const GemmParams& p, int tile, int& tm, int& tn) {
+    if (p.group_m <= 1) {
+        tm = tile / p.tiles_n;
+        tn = tile % p.tiles_n;
+        return;
+    }
+    const int band = p.group_m * p.tiles_n;
+    const int g = tile / band;
+    const int first = g * p.group_m;
+    const int rows = p.tiles_m - first < p.group_m ? p.tiles_m - first : p.group_m;
+    const int r = tile - g * band;
+    tm = first + r % rows;
+    tn = r / rows;
+}
 
 // Epilogues fused into the CTA-pair GEMM:
 //  SWIGLU : B = [w1; w3] ([2F, K], F = epi_i0). A tile is 128 gate columns AND the matching 128 up

@@ -38,6 +38,38 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn, bn):
     ops.check_status()
 
 
+@pytest.mark.parametrize("M", [2304, 4352])
+def test_gemm_banded_tile_order(M):
+    """A B operand of 48 MB or more switches the CTA-pair kernel to tile numbering in bands of 16 tile rows: 9 rows
+    (one short band) and 17 rows (a full band and a band of one), plain, residual and fp32 epilogues."""
+    torch.manual_seed(0)
+    dev = "cuda"
+    N, K = 12544, 2048                                              # B = 51 MB, 49 tile columns
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device=dev) * K ** -0.5).bfloat16()
+    ref = a.float() @ b.float().t()
+    out = ops.gemm(a, b)
+    r = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+    out_r = ops.gemm(a, b, residual=r)
+    out_f = ops.gemm(a, b, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel(out, ref) < 1e-2 and _rel(out_r, ref + r.float()) < 1e-2 and _rel(out_f, ref) < 1e-3
+    # the same through the N-major layout of B (input-gradient form) and with the SwiGLU epilogue (w13 = 50 MB)
+    bt = b.t().contiguous()
+    assert _rel(ops.gemm(a, bt, b_mn=True), ref) < 1e-2
+    F = 6144
+    w13 = (torch.randn(2 * F, K, device=dev) * K ** -0.5).bfloat16()
+    h13 = torch.empty(M, 2 * F, device=dev, dtype=torch.bfloat16)
+    act = torch.empty(M, F, device=dev, dtype=torch.bfloat16)
+    ops.gemm_swiglu(a, w13, h13, act)
+    ref13 = a.float() @ w13.float().t()
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel(h13, ref13) < 1e-2
+    assert _rel(act, torch.nn.functional.silu(ref13[:, :F]) * ref13[:, F:]) < 1e-2
+
+
 @pytest.mark.parametrize("M,F,K", [(1024, 256, 192), (2000, 1024, 512), (4096, 4096, 1024)])
 def test_gemm_fused_swiglu_epilogues(M, F, K):
     """SwiGLU forward and backward fused into the CTA-pair GEMM epilogue vs plain fp32 math."""
