@@ -638,11 +638,12 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
 // CTA pairs, which is free while B stays in L2; a B operand that does not fit there (48 MB and more: the 10B model's
 // w13 and head, the 150M model's head) would be streamed from HBM tiles_m / (rows per wave) times, so such products
 // use bands of 16 rows: [8192 x 128256 x 4096] 8.22 -> 5.81 ms, [8192 x 28672 x 4096] 1.61 -> 1.25 ms, while products
-// with a small B lose 1-2 % to banding and keep the row-major order. PRIME_B200_GEMM_GROUP_M overrides (measurements).
+// with a small B, or with so few tile columns that a wave spans several tile rows anyway, lose 1-2 % to banding and
+// keep the row-major order. PRIME_B200_GEMM_GROUP_M overrides (measurements).
 static int tile_band_rows(int tiles_m, int tiles_n, long long b_bytes) {
     static const int forced = [] { const char* e = getenv("PRIME_B200_GEMM_GROUP_M"); return e ? atoi(e) : 0; }();
     if (forced > 0) return forced;
-    return (b_bytes >= (48ll << 20) && tiles_n > 8 && tiles_m >= 8) ? 16 : 1;
+    return (b_bytes >= (48ll << 20) && tiles_n >= 32 && tiles_m >= 8) ? 16 : 1;
 }
 
 template <bool A_MN, bool B_MN, bool GATHER = false, int EPI = GEMM_EPI_NONE>
