@@ -167,7 +167,7 @@ def _copy_tree(src: str, dst: str) -> None:
     """Copy a step directory; ``dst`` may be any fsspec URL."""
     if "://" not in dst:
         os.makedirs(os.path.dirname(dst) or ".", exist_ok=True)
-        tmp = dst + ".partial"
+        tmp = f"{dst}.partial.{os.getpid()}"      # unique per copier: two jobs never share a temporary tree
         shutil.rmtree(tmp, ignore_errors=True)
         shutil.copytree(src, tmp)
         shutil.rmtree(dst, ignore_errors=True)
@@ -227,6 +227,22 @@ class LiveRecoverySidecar:
     def stop(self):
         self.httpd.shutdown()
         self.httpd.server_close()
+
+
+def _default_sidecar_addr() -> str:
+    """Address the sidecar binds when ZERO_BAND_LIVE_RECO_ADDR is unset: the interface the worker group talks over
+    (loopback for single-host groups, the GLOO_SOCKET_IFNAME interface otherwise); every interface only as a last
+    resort."""
+    if os.environ.get("GLOBAL_ADDR", "127.0.0.1") in ("localhost", "127.0.0.1"):
+        return "127.0.0.1"
+    ifname = os.environ.get("GLOO_SOCKET_IFNAME")
+    if ifname:
+        try:
+            from .utils.ip import get_ip_address
+            return get_ip_address(ifname)
+        except OSError:
+            pass
+    return "0.0.0.0"
 
 
 def download_live_ckpt(url: str, destination: str) -> str:
@@ -356,7 +372,8 @@ class CkptManager:
             data_dir = os.path.join(ckpt_path, "data")
             self.save_data(data_dir, self.dataloader, self.world_info.local_rank)
             non_error_barrier(self.process_group)
-            if self.config.remote_data_path is not None:
+            # after the barrier data_dir holds every local rank's file: one copier per destination, from local rank 0
+            if self.config.remote_data_path is not None and self.world_info.local_rank == 0:
                 base = os.path.join(self.config.remote_data_path, f"data_{self.data_rank}")
                 for name in (f"step_{self.training_progress.step}", "latest"):
                     self._spawn(_copy_tree, (data_dir, os.path.join(base, name)), blocking=False)
@@ -392,6 +409,9 @@ class CkptManager:
         if self._sidecar is not None:
             self._sidecar.stop()
             self._sidecar = None
+        # the staged copy lives in RAM (/dev/shm): once the persistence jobs have joined it is on disk, so free it
+        if self.use_staging and self._staging_root is not None and self.world_info.local_rank == 0:
+            shutil.rmtree(self._staging_root, ignore_errors=True)
 
     def __del__(self):
         try:
@@ -428,7 +448,7 @@ class CkptManager:
                 p_off.data.copy_(t)
         if self.diloco_offloaded_optimizer is not None:
             with open(os.path.join(resume_ckpt_path, f"__{world_info.local_rank}_0.pt"), "rb") as f:
-                rank_state = torch.load(f, weights_only=False)
+                rank_state = torch.load(f, weights_only=True)     # tensors and plain values only
             OuterOptimizerWrapper(self.diloco_offloaded_optimizer).load_state_dict(rank_state["optimizer"])
         if not skip_dataloader:
             if self.config.remote_data_load:
@@ -451,7 +471,7 @@ class CkptManager:
             return self._sidecar.port if self._sidecar is not None else None
         base = int(os.environ.get("ZERO_BAND_LIVE_RECO_PORT", "0"))
         port = base + self.world_info.local_rank if base else 0
-        self._sidecar = LiveRecoverySidecar(self._staging_root, os.environ.get("ZERO_BAND_LIVE_RECO_ADDR", "0.0.0.0"), port)
+        self._sidecar = LiveRecoverySidecar(self._staging_root, os.environ.get("ZERO_BAND_LIVE_RECO_ADDR", _default_sidecar_addr()), port)
         return self._sidecar.port
 
     def recover_from_sidecar(self, url: str, scratch_dir: str | None = None) -> None:

@@ -555,7 +555,9 @@ class ElasticDeviceMesh:
         for a in live:
             for b in live:
                 self.god_store.set(f"ping_{a}_{b}", str(PING_UNKNOWN))
-        for i in range(1, n):
+        # barrier_0 too: a failed monitored barrier leaves "error" there, and the survivors' retry (same flag)
+        # must not read that stale value
+        for i in range(n):
             self.global_store.set(f"barrier_{i}", "null")
         self.global_store.set("world_size", str(n))
         self.global_store.set("mesh_count", str(self.mesh_count + 1))

@@ -17,7 +17,9 @@ class MetricLogger(Protocol):
 class WandbMetricLogger:
     def __init__(self, project, config, resume: bool):
         import wandb
-        run_name = config.get("run_name") if isinstance(config, dict) else None
+        # the trainer passes {"config": <Config dump>, "world_info": ...}; the run name lives in the inner dict
+        inner = config.get("config", config) if isinstance(config, dict) else {}
+        run_name = inner.get("run_name") if isinstance(inner, dict) else None
         wandb.init(project=project, config=config, name=run_name, resume="auto" if resume else None)
 
     def log(self, metrics: dict[str, Any]):

@@ -15,8 +15,12 @@ def wget(source: str, destination: str, timeout: float = 600.0) -> list[str]:
     with urllib.request.urlopen(source + "?list=1", timeout=timeout) as r:
         files = json.loads(r.read().decode())
     os.makedirs(destination, exist_ok=True)
+    root = os.path.realpath(destination)
     for rel in files:
-        dst = os.path.join(destination, rel)
+        # the listing comes from a peer: a name may only land inside `destination`
+        dst = os.path.realpath(os.path.join(root, rel))
+        if not isinstance(rel, str) or os.path.isabs(rel) or os.path.commonpath([root, dst]) != root or dst == root:
+            raise ValueError(f"refusing to download {rel!r}: it would be written outside {destination}")
         os.makedirs(os.path.dirname(dst) or destination, exist_ok=True)
         with urllib.request.urlopen(source + rel, timeout=timeout) as r, open(dst, "wb") as f:
             shutil.copyfileobj(r, f, length=8 << 20)

@@ -117,7 +117,10 @@ def _barrier_worker(role):
     except RuntimeError:
         failed = True
     changed = edm.maybe_reinit_global_pg(admit_joiners=False)
-    out = (failed, changed, edm.global_pg.size())
+    # the retry of the outer step: same flag again, now among the survivors, then the reduction itself
+    edm.monitored_barrier("x")
+    total = _allreduce_check(edm, 1 + edm.world_info.global_rank)
+    out = (failed, changed, edm.global_pg.size(), total)
     _finish(edm)
     return out
 
@@ -192,8 +195,8 @@ def test_monitored_barrier_evicts_late_worker():
     [p.start() for p in procs]
     out = _collect(procs, q, 3)
     for uid in ("w0", "w1"):
-        failed, changed, size = out[uid]
-        assert failed is True and changed is True and size == 2
+        failed, changed, size, total = out[uid]
+        assert failed is True and changed is True and size == 2 and total == 3.0
 
 
 def test_ring_order_solver():

@@ -266,3 +266,37 @@ def test_host_library_under_sanitizers(sanitizer, tmp_path):
     run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert run.returncode == 0, (run.stdout + run.stderr)[-3000:]
     assert "0 failure(s)" in run.stdout
+
+
+def test_wget_refuses_names_outside_destination(tmp_path, monkeypatch):
+    """A peer's listing is untrusted: entries that would land outside the destination are refused."""
+    import io
+    import json
+    import urllib.request
+
+    from prime_b200.utils import wget as W
+
+    def fake_open(url, timeout=None):
+        if url.endswith("?list=1"):
+            return io.BytesIO(json.dumps(["ok.bin", "../escape.bin"]).encode())
+        return io.BytesIO(b"data")
+
+    monkeypatch.setattr(urllib.request, "urlopen", fake_open)
+    dest = tmp_path / "dst"
+    with pytest.raises(ValueError):
+        W.wget("http://127.0.0.1:1/latest/", str(dest))
+    assert (dest / "ok.bin").read_bytes() == b"data" and not (tmp_path / "escape.bin").exists()
+    monkeypatch.setattr(urllib.request, "urlopen", lambda url, timeout=None: io.BytesIO(json.dumps(["/abs.bin"]).encode()))
+    with pytest.raises(ValueError):
+        W.wget("http://127.0.0.1:1/latest/", str(dest))
+
+
+def test_wandb_logger_reads_run_name_from_inner_config(monkeypatch):
+    import sys
+    import types
+    seen = {}
+    fake = types.SimpleNamespace(init=lambda **kw: seen.update(kw), log=lambda m: None, finish=lambda: None)
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    from prime_b200.utils.metric_logger import WandbMetricLogger
+    WandbMetricLogger(project="p", config={"config": {"run_name": "r1"}, "world_info": {}}, resume=False)
+    assert seen["name"] == "r1"
