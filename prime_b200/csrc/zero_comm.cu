@@ -6,10 +6,11 @@
 // 365-372); here the collective is executed by the kernel that also does the math:
 //
 //   pb_zero_reduce_grads : reduce-scatter by PULL. For every segment this rank owns, load the
-//                          slice from all W ranks with plain P2P ld.global (rotated start peer so
-//                          the W ranks do not hit the same GPU at once), sum in fp32 in fixed rank
-//                          order (bit-identical on every run), scale, write the fp32 shard and
-//                          accumulate the sum of squares needed for global-norm clipping.
+//                          slice from all W ranks with plain P2P ld.global (every thread has the
+//                          loads of all W peers in flight before its first add, so all links are
+//                          busy at once), sum in fp32 in fixed rank order (bit-identical on every
+//                          run), scale, write the fp32 shard and accumulate the sum of squares
+//                          needed for global-norm clipping.
 //   pb_zero_adamw_gather : sharded AdamW fused with the all-gather by PUSH. Each updated value is
 //                          converted to bf16 and stored straight into every rank's parameter
 //                          buffer with P2P st.global, so no gathered copy is ever staged.
@@ -57,7 +58,7 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 
 // pads[r] points at rank r's flag pad: int[slots][MAX_RANKS]. Thread t signals peer t and waits
 // for peer t's signal in its own pad. Epochs only grow, so no reset race exists.
-__global__ void peer_barrier_kernel(PeerTable pads, int slot, int epoch, int* status) {
+__global__ void peer_barrier_kernel(PeerTable pads, int slot, int epoch, int* status, unsigned long long budget_ns) {
     const int t = threadIdx.x;
     if (t >= pads.world) return;
     __threadfence_system();
@@ -66,7 +67,7 @@ __global__ void peer_barrier_kernel(PeerTable pads, int slot, int epoch, int* st
     const int* mine = reinterpret_cast<const int*>(pads.ptr[pads.rank]) + slot * MAX_RANKS + t;
     const uint64_t t0 = globaltimer_ns();
     while (ld_acquire_sys(mine) < epoch) {
-        if (globaltimer_ns() - t0 > PB_WAIT_BUDGET_NS) {
+        if (globaltimer_ns() - t0 > budget_ns) {
             if (status) atomicCAS(status, 0, PB_ERR_TIMEOUT_PEER | (t << 8));
             return;
         }
@@ -78,7 +79,8 @@ __global__ void peer_barrier_kernel(PeerTable pads, int slot, int epoch, int* st
 // data pads: float[slots][2 (epoch parity)][MAX_RANKS][8]; the parity double-buffer lets a fast rank start
 // the next reduction while a slow one still sums the previous values
 __global__ void allreduce_scalars_kernel(PeerTable flag_pads, PeerTable data_pads, int slot, int epoch,
-                                         const float* __restrict__ in, float* __restrict__ out, int n, int* status) {
+                                         const float* __restrict__ in, float* __restrict__ out, int n, int* status,
+                                         unsigned long long budget_ns) {
     const int t = threadIdx.x;
     if (t < flag_pads.world) {
         float* remote = reinterpret_cast<float*>(data_pads.ptr[t]) + ((slot * 2 + (epoch & 1)) * MAX_RANKS + flag_pads.rank) * 8;
@@ -89,7 +91,7 @@ __global__ void allreduce_scalars_kernel(PeerTable flag_pads, PeerTable data_pad
         const uint64_t t0 = globaltimer_ns();
         bool ok = true;
         while (ld_acquire_sys(mine) < epoch) {
-            if (globaltimer_ns() - t0 > PB_WAIT_BUDGET_NS) {
+            if (globaltimer_ns() - t0 > budget_ns) {
                 if (status) atomicCAS(status, 0, PB_ERR_TIMEOUT_PEER | (t << 8));
                 ok = false;
                 break;
@@ -166,6 +168,7 @@ __global__ void __launch_bounds__(256) zero_reduce_grads_kernel(PeerTable peers,
         const bool vec_ok = (fo % 8 == 0) && (segs.shard_off[s] % 4 == 0) && sizeof(G) == 2;
         const long long nvec = vec_ok ? n / 8 : 0;
         if (W <= 4) ss += reduce_vectors<4, 4>(peers, W, fo, nvec, scale, dst, b, nb);
+        else if (W <= 8) ss += reduce_vectors<8, 2>(peers, W, fo, nvec, scale, dst, b, nb);
         else ss += reduce_vectors<MAX_RANKS, 1>(peers, W, fo, nvec, scale, dst, b, nb);
         for (long long i = nvec * 8 + b * blockDim.x + threadIdx.x; i < n; i += nb * blockDim.x) {
             float acc = 0.f;
@@ -333,9 +336,19 @@ extern "C" int pb_zero_cta_ranges(int nseg, const long long* numel, int ctas, in
     return sg.cta_begin[nseg];
 }
 
+// How long a peer wait may spin before it gives up with PB_ERR_TIMEOUT_PEER. Passed to the kernels as an argument on
+// every launch; the default is the compile-time budget of the other bounded waits (2 s).
+static unsigned long long g_peer_wait_budget_ns = PB_WAIT_BUDGET_NS;
+extern "C" int pb_set_peer_wait_budget_ns(long long ns) {
+    if (ns <= 0) return -1;
+    g_peer_wait_budget_ns = (unsigned long long)ns;
+    return 0;
+}
+extern "C" long long pb_get_peer_wait_budget_ns() { return (long long)g_peer_wait_budget_ns; }
+
 extern "C" int pb_peer_barrier(void* const* pad_ptrs, int world, int rank, int slot, int epoch, int* status, void* stream) {
     if (world > MAX_RANKS) return -1;
-    peer_barrier_kernel<<<1, 32, 0, ST(stream)>>>(make_peers(pad_ptrs, world, rank), slot, epoch, status);
+    peer_barrier_kernel<<<1, 32, 0, ST(stream)>>>(make_peers(pad_ptrs, world, rank), slot, epoch, status, g_peer_wait_budget_ns);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 
@@ -343,7 +356,7 @@ extern "C" int pb_allreduce_scalars(void* const* flag_pads, void* const* data_pa
                                     const float* in, float* out, int n, int* status, void* stream) {
     if (world > MAX_RANKS || n > 8) return -1;
     allreduce_scalars_kernel<<<1, 32, 0, ST(stream)>>>(make_peers(flag_pads, world, rank), make_peers(data_pads, world, rank), slot,
-                                                       epoch, in, out, n, status);
+                                                       epoch, in, out, n, status, g_peer_wait_budget_ns);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 

@@ -87,6 +87,9 @@ class LocalComm:
     def barrier(self, stream=None):
         pass
 
+    def host_barrier(self):
+        pass
+
     def allreduce_scalars(self, src: torch.Tensor, dst: torch.Tensor, n: int):
         dst[:n].copy_(src[:n])
 
@@ -200,12 +203,16 @@ class FusedLlama:
                 self.params[s.full_offset: s.full_offset + s.numel].copy_(v.reshape(-1).to(torch.bfloat16))
             return
         lib = native.cuda()
+        # publishing happens at start-up, after a checkpoint load and after an outer step, where ranks can be seconds
+        # apart: meet on the host first so the bounded device barriers below only ever wait for kernel skew
+        self.comm.host_barrier()
         self.comm.barrier()
         for g, sa in enumerate(self._segs):
             if sa.n:
                 check(lib.pb_zero_push_params(self._peer_params, self.world, self.rank, sa.n, sa.full, sa.shard, sa.numel,
                                               ptr(self.master), self.comm_ctas, stream_ptr()), "pb_zero_push_params")
         self.comm.barrier()
+        K.check_status(self.device)   # a peer that never arrived: raise here rather than train on a partial replica
 
     # ------------------------------------------------------------------------------------------
     # workspace
@@ -447,7 +454,16 @@ class FusedLlama:
             total[1] += out["z_loss"] / n_micro
         norm = self.optimizer_step(lr, betas, eps, weight_decay, max_norm)
         if sync_loss:
-            host = torch.stack([total[0], total[1], norm]).tolist()   # the step's only device->host read
+            # the step's only device->host read; the device status word rides along, so a peer wait that gave up
+            # (PB_ERR_TIMEOUT_PEER) surfaces as an exception of this step instead of a silently partial update
+            st = K.status_word(self.device) if self.device.type == "cuda" else None
+            vals = [total[0], total[1], norm] + ([st[0].to(torch.float32)] if st is not None else [])
+            host = torch.stack(vals).tolist()
+            if st is not None and host[3] != 0.0:
+                code = int(host[3])
+                st.zero_()
+                raise native.NativeError(f"train_step: device kernel reported error code {code & 0xff} (peer/cta {code >> 8}); "
+                                         "the update of this step is not valid")
             return host[0], host[2]
         return total[0], norm
 

@@ -107,6 +107,9 @@ class NvlinkWorkerGroup:
             check(lib.pb_dl_stage_c(self._pq, self._plut, self._pq2, self._plut2, self.comm.world, self.comm.rank, n, None, None, None,
                                     0.0, 0.0, ptr(x), stream_ptr()), "pb_dl_stage_c")
             self.comm.barrier(slot=3)
+            # a peer wait that gave up must fail this reduction (the caller's retry path handles the exception)
+            from ..ops.kernels import check_status
+            check_status(self.device)
         if not tensor.is_cuda:
             tensor.copy_(x)
         return None

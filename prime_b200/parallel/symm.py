@@ -46,6 +46,13 @@ class SymmComm:
         dist.barrier(self.group)
         torch.cuda.synchronize()
 
+    def host_barrier(self) -> None:
+        """Host-level rendezvous of the group (not stream-ordered). Used before the first device barrier of a phase
+        whose ranks may arrive seconds apart (start-up, checkpoint load): the device barriers give up after their
+        wait budget, the host one does not."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
     def _alloc_raw(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         t = self._symm.empty(numel, dtype=dtype, device=self.device)
         t.zero_()

@@ -67,3 +67,84 @@ def test_engine_gpu_loss_decreases_and_logits():
 def test_smoke_entry():
     import __graft_entry__ as ge
     ge.smoke()
+
+
+class _SilentPeerComm:
+    """Single-rank communicator whose device barrier waits for a second 'peer' that never signals: pad 1 is this
+    GPU's own zero-filled memory. The wait runs out after its (short) budget and the kernel returns with
+    PB_ERR_TIMEOUT_PEER in the status word; nothing traps, faults or spins forever."""
+    world, rank = 1, 0
+
+    def __init__(self, device):
+        import ctypes as C
+        from prime_b200.engine.fused_llama import LocalComm
+        self._local = LocalComm()
+        self.device = torch.device(device)
+        self.pads = torch.zeros(2, 64 * 16, dtype=torch.int32, device=device)
+        self._ptrs = (C.c_void_p * 2)(self.pads[0].data_ptr(), self.pads[1].data_ptr())
+        self.epoch = 0
+        self.silent = False
+
+    def alloc(self, *a, **k):
+        return self._local.alloc(*a, **k)
+
+    def peer_ptrs(self, t):
+        return self._local.peer_ptrs(t)
+
+    def host_barrier(self):
+        pass
+
+    def allreduce_scalars(self, src, dst, n):
+        dst[:n].copy_(src[:n])
+
+    def barrier(self, stream=None):
+        if not self.silent:
+            return
+        from prime_b200 import native
+        from prime_b200.native import check, ptr, stream_ptr
+        from prime_b200.ops.kernels import status_word
+        self.epoch += 1
+        check(native.cuda().pb_peer_barrier(self._ptrs, 2, 0, 0, self.epoch, ptr(status_word(self.device)), stream_ptr()),
+              "pb_peer_barrier")
+
+
+def test_peer_wait_runs_out_and_train_step_raises():
+    """A device-side wait for a peer that never arrives gives up after its budget, the status word carries
+    PB_ERR_TIMEOUT_PEER, train_step turns it into an exception, and the context keeps working afterwards."""
+    import time
+    from prime_b200 import native
+    from prime_b200.ops.kernels import status_word
+    lib = native.cuda()
+    native.register_cuda_sigs({"pb_set_peer_wait_budget_ns": [native.i64], "pb_get_peer_wait_budget_ns": []})
+    lib.pb_get_peer_wait_budget_ns.restype = __import__("ctypes").c_longlong
+    old = lib.pb_get_peer_wait_budget_ns()
+    assert old == 2_000_000_000
+    assert lib.pb_set_peer_wait_budget_ns(20_000_000) == 0            # 20 ms
+    try:
+        args = _args()
+        comm = _SilentPeerComm("cuda")
+        eng = FusedLlama(args, device="cuda", comm=comm, ce_chunk_tokens=256)
+        eng.init_weights(seed=0)
+        tok = torch.randint(0, args.vocab_size, (2, 257))
+        x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+        loss0, _ = eng.train_step(x, y, lr=1e-3)                       # healthy step
+        comm.silent = True
+        t0 = time.perf_counter()
+        with pytest.raises(native.NativeError, match="error code 5"):
+            eng.train_step(x, y, lr=1e-3)
+        assert time.perf_counter() - t0 < 5.0                          # two 20 ms waits, not a hang
+        assert int(status_word(torch.device("cuda", 0)).item()) == 0   # cleared by the raise
+        comm.silent = False
+        loss1, _ = eng.train_step(x, y, lr=1e-3)                       # the context is still usable
+        assert loss1 == loss1 and loss1 < loss0 + 1.0
+        # the bare kernel: status word holds code 5 with the silent peer's index in the upper bits
+        comm.silent = True
+        comm.barrier()
+        torch.cuda.synchronize()
+        code = int(status_word(torch.device("cuda", 0)).item())
+        assert code & 0xff == 5 and code >> 8 == 1
+        with pytest.raises(native.NativeError):
+            check_status()
+        check_status()
+    finally:
+        lib.pb_set_peer_wait_budget_ns(old)

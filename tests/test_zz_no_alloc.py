@@ -56,6 +56,10 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert torch.cuda.memory_allocated() == before
         assert _rel(dx, dx_ref) < 1e-2, f"call {call}: dx"
         assert _rel(dw, dw_ref) < 1e-3, f"call {call}: dw"
+        # and against the fp32 PyTorch twin of the op on the CPU, so this test stands on its own
+        dw_cpu = torch.zeros(N, dtype=torch.float32)
+        dx_cpu = ops.rmsnorm_bwd(x.cpu(), w.cpu(), rstd.cpu(), dy.cpu(), dw_cpu, dres=dres.cpu(), accumulate_dw=False)
+        assert _rel(dx.cpu(), dx_cpu) < 1e-2 and _rel(dw.cpu(), dw_cpu) < 1e-2, f"call {call}: CPU twin"
 
 
 def test_noalloc_rejects_rows_wider_than_the_builtin_scratch():
