@@ -34,6 +34,7 @@ import os
 import shutil
 import threading
 import time
+import urllib.request
 import uuid
 import warnings
 from dataclasses import dataclass
@@ -196,6 +197,16 @@ class _SidecarHandler(http.server.SimpleHTTPRequestHandler):
         pass
 
     def do_GET(self):
+        if self.path.endswith("?resolve=1"):
+            # the real name behind a symlinked directory ("latest" -> "step_N"), so a client can pin one step
+            real = os.path.basename(os.path.realpath(self.translate_path(self.path.split("?", 1)[0])))
+            body = json.dumps(real).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+            return
         if self.path.endswith("?list=1"):
             root = self.translate_path(self.path.split("?", 1)[0])
             files = []
@@ -248,6 +259,16 @@ def _default_sidecar_addr() -> str:
 def download_live_ckpt(url: str, destination: str) -> str:
     """Fetch a peer's newest staged checkpoint (``http://addr:port/latest/``) into ``destination``."""
     from .utils.wget import wget
+    # pin the step behind ".../latest/" first: the link may move to a newer step while the files are being fetched
+    base = url.rstrip("/")
+    if base.endswith("/latest"):
+        try:
+            with urllib.request.urlopen(base + "/?resolve=1", timeout=60) as r:
+                step = json.loads(r.read().decode())
+            if isinstance(step, str) and step.startswith("step_"):
+                url = base[: -len("latest")] + step + "/"
+        except (OSError, ValueError):
+            pass
     wget(url, destination)
     return destination
 

@@ -450,14 +450,20 @@ class ElasticDeviceMesh:
         self._create_global_pg()
         if self._global_leader:
             self.global_store.set("status", "running")
-            self.global_store.set("resolved_time", uuid4().hex)
+            self._resolve_seq = 0
+            self.global_store.set("resolved_time", f"0:{uuid4().hex}")
         self.global_status = "running"
-        self._last_resolved_time = self._wait_key("resolved_time")
+        self._last_resolve_seq = self._resolution_seq(self._wait_key("resolved_time"))
         self._start_heartbeat()
         self._logger.info(f"Elastic Device mesh init done with {self.global_pg.size()} peers in {time.perf_counter() - t0} seconds")
         if wi.local_rank == 0:
             self._start_bandwidth_sink()
         self._evicted_nodes: list[str] = []
+
+    @staticmethod
+    def _resolution_seq(value: str) -> int:
+        """Sequence number of a ``resolved_time`` value (``"<seq>:<uuid>"``)."""
+        return int(value.split(":", 1)[0])
 
     def _wait_key(self, key: str) -> str:
         deadline = time.monotonic() + self.store_timeout.total_seconds()
@@ -571,15 +577,19 @@ class ElasticDeviceMesh:
         t0 = time.perf_counter()
         if self._global_leader:
             self._resolve_world(admit_joiners=admit_joiners)
-            self.global_store.set("resolved_time", uuid4().hex)
-            self._last_resolved_time = self._get("resolved_time")
+            self._resolve_seq += 1
+            self.global_store.set("resolved_time", f"{self._resolve_seq}:{uuid4().hex}")
         else:
+            # Resolutions are counted, not just noticed: the leader bumps the sequence number once per call and does
+            # not wait for anyone when membership is unchanged, so it can be two calls ahead of a worker that was busy
+            # (writing a checkpoint, say). A worker that only waited for "the value changed" would take both bumps for
+            # one and then wait for a third that never comes. One resolution of the leader's lead is kept in credit.
             deadline = time.monotonic() + self.pg_timeout.total_seconds()
-            while (ans := self._get("resolved_time")) == self._last_resolved_time:
+            while (seq := self._resolution_seq(self._get("resolved_time"))) <= self._last_resolve_seq:
                 if time.monotonic() > deadline:
                     raise TimeoutError("the leader did not resolve the world in time")
                 time.sleep(self.polling_interval)
-            self._last_resolved_time = ans
+            self._last_resolve_seq = max(self._last_resolve_seq + 1, seq - 1)
         self._logger.debug("World resolved in %s seconds", time.perf_counter() - t0)
         if self._get("status") == "running":
             return False

@@ -126,6 +126,11 @@ class CkptConfig(BaseConfig):
     resume: str | None = None
     skip_dataloader: bool = False
     live_recovery_rank_src: int | None = None
+    # joiner side of the sidecar recovery: URL of a running worker's sidecar (".../latest/"), or "auto" to look the
+    # address up in the worker-group store (source = live_recovery_rank_src, default rank 0). The joiner downloads the
+    # newest staged checkpoint, skips the inner steps of that outer iteration and enters the outer step with a zero
+    # pseudo-gradient.
+    live_recovery_url: str | None = None
     data_path: str | None = None
     token_count: int | None = None
 
@@ -186,6 +191,8 @@ class Config(BaseConfig):
     def validate_live_recovery_rank_src(self):
         if self.ckpt is not None and self.ckpt.live_recovery_rank_src is not None and self.diloco is None:
             raise ValueError("live_recovery_rank_src is only supported with diloco")
+        if self.ckpt is not None and self.ckpt.live_recovery_url is not None and self.diloco is None:
+            raise ValueError("live_recovery_url is only supported with diloco")
         return self
 
 

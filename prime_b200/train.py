@@ -75,6 +75,29 @@ def _get_tokenizer(config: Config):
     return AutoTokenizer.from_pretrained(name, use_fast=True)
 
 
+def _resolve_sidecar_url(config: Config, edm: ElasticDeviceMesh) -> str:
+    """``ckpt.live_recovery_url`` as given, or for "auto" the address the source worker published in the store."""
+    url = config.ckpt.live_recovery_url
+    if url != "auto":
+        return url
+    src = config.ckpt.live_recovery_rank_src or 0
+    uid = edm.global_store.get(f"gid_{src}").decode()
+    return f"http://{edm.global_store.get(f'sidecar_{uid}').decode()}/latest/"
+
+
+def _recover_from_sidecar_with_retry(ckpt_manager: CkptManager, url: str, limit_s: float) -> None:
+    """The source may not have staged a checkpoint yet (it saves at outer-step boundaries): poll until it has."""
+    deadline = time.monotonic() + limit_s
+    while True:
+        try:
+            ckpt_manager.recover_from_sidecar(url)
+            return
+        except Exception:  # noqa: BLE001
+            if time.monotonic() > deadline:
+                raise
+            time.sleep(1.0)
+
+
 def train(config: Config) -> None:
     world_info = get_world_info()
     logger = get_logger(config)
@@ -111,9 +134,11 @@ def train(config: Config) -> None:
     num_flop_per_token = get_num_flop_per_token(num_params, margs, config.data.seq_length)
     logger.info(f"Number of parameters: {num_params}")
 
+    # a joiner that recovers from a sidecar does not ask the source for a point-to-point transfer
+    sidecar_join = config.ckpt.live_recovery_url is not None
     with sw.record_block("Elastic Device Mesh"):
         elastic_device_mesh = ElasticDeviceMesh(enable=config.diloco is not None,
-                                                live_recovery_rank_src=config.ckpt.live_recovery_rank_src)
+                                                live_recovery_rank_src=None if sidecar_join else config.ckpt.live_recovery_rank_src)
 
     sched = partial(get_scheduler, config.optim.sched_type, num_warmup_steps=config.optim.warmup_steps,
                     num_stable_steps=config.optim.stable_steps, num_training_steps=config.optim.total_steps)
@@ -149,7 +174,15 @@ def train(config: Config) -> None:
                                process_group=elastic_device_mesh.local_pg if world_info.workers_in_job > 1 else None,
                                subdir=f"worker_{world_info.global_rank}" if world_info.workers_in_job > 1 else None)
     if diloco is not None and config.ckpt.path is not None:
-        ckpt_manager.start_sidecar()
+        port = ckpt_manager.start_sidecar()
+        if port is not None and elastic_device_mesh.enable:
+            # address book for joiners: same-shard ranks of every worker share one store, so one key per worker id
+            from .checkpoint import _default_sidecar_addr
+            addr = os.environ.get("ZERO_BAND_LIVE_RECO_ADDR") or _default_sidecar_addr()
+            if addr == "0.0.0.0":
+                from .collectives import _my_ip
+                addr = _my_ip()
+            elastic_device_mesh.global_store.set(f"sidecar_{world_info.global_unique_id}", f"{addr}:{port}")
 
     metric_logger = None
     if world_info.rank == 0:
@@ -172,7 +205,8 @@ def train(config: Config) -> None:
     perf_counter = PerfCounter(window_size=10)
     device_meter = utils.DeviceThroughputMeter(window_size=10)
     logger.debug("Finished setup in %f seconds", sw.elapsed())
-    need_live_recovery = config.ckpt.live_recovery_rank_src is not None
+    need_live_recovery = config.ckpt.live_recovery_rank_src is not None and not sidecar_join
+    need_sidecar_recovery = sidecar_join
     fake_outer_step = False
 
     while True:
@@ -180,7 +214,18 @@ def train(config: Config) -> None:
             logger.info(f"outer_step step: {training_progress.outer_step}")
         time_start_outer = time.perf_counter()
         if diloco is not None:
-            if not need_live_recovery:
+            if need_sidecar_recovery:
+                # README join: fetch the newest staged checkpoint of a running worker over HTTP while the members train,
+                # skip this outer iteration's inner steps and enter the outer step with a zero pseudo-gradient
+                t0 = time.perf_counter()
+                url = _resolve_sidecar_url(config, elastic_device_mesh)
+                logger.info(f"Start live recovery from sidecar {url}")
+                _recover_from_sidecar_with_retry(ckpt_manager, url, elastic_device_mesh.pg_timeout.total_seconds())
+                log_hash_training_state(config, backend, diloco, metric_logger, step=training_progress.step, id="live_reco_recv")
+                need_sidecar_recovery = False
+                fake_outer_step = True
+                logger.info("sidecar live recovery done in %f", time.perf_counter() - t0)
+            elif not need_live_recovery:
                 elastic_device_mesh.maybe_reinit_global_pg(admit_joiners=True)
                 dest = elastic_device_mesh.live_recovery.should_send_ckpt_to()
                 if dest is not None:
@@ -197,7 +242,14 @@ def train(config: Config) -> None:
                     ckpt_manager.remote_data_load()
                 logger.info("live recovery done in %f", time.perf_counter() - t0)
 
-        for inner_step in range(num_inner_steps):
+        if fake_outer_step:
+            # the members run these steps; the joiner only keeps its counters and schedule aligned with theirs
+            for _ in range(num_inner_steps):
+                backend.lr_scheduler.step()
+            training_progress.step += num_inner_steps
+            training_progress.total_tokens += (num_inner_steps * config.data.seq_length * config.optim.batch_size
+                                               * elastic_device_mesh.global_pg.size())
+        for inner_step in range(0 if fake_outer_step else num_inner_steps):
             sw.start("inner_step")
             with sw.record_block("Load batch"):
                 batch = next(train_iter)

@@ -128,3 +128,59 @@ def test_checkpoint_resume_equivalence(tmp_path):
     for s in lr_:
         assert abs(lf[s]["Loss"] - lr_[s]["Loss"]) < 1e-3
         assert lf[s]["inner_lr"] == lr_[s]["inner_lr"] and lf[s]["total_tokens"] == lr_[s]["total_tokens"]
+
+
+def test_late_joiner_recovers_from_sidecar_and_enters_with_zero_pseudo_gradient(tmp_path):
+    """Two workers train with a checkpoint staged at every outer step; a third starts later with
+    ``--ckpt.live_recovery_url auto``: it downloads the newest staged checkpoint from worker 0's sidecar while the
+    members keep training, skips the inner steps of that outer iteration, contributes a zero pseudo-gradient, and
+    from that outer step on holds the same outer model and optimizer state as the members."""
+    import time
+    ports = get_random_available_port_list(5)
+    total = 24
+    common = ["@configs/debug/diloco.toml", "--optim.total_steps", str(total), "--diloco.inner_steps", "2", "--train.micro_bs", "4",
+              "--optim.batch_size", "8", "--train.log_model_hash", "--data.seq_length", "128", "--ckpt.interval", "2", "--ckpt.topk", "2"]
+    genv = {"GLOBAL_ADDR": "127.0.0.1", "GLOBAL_PORT": str(ports[0]), "GLOBAL_WORLD_SIZE": "2",
+            "ZERO_BAND_GLOBAL_PG_TIMEOUT_SECONDS": "120", "PRIME_B200_CKPT_STAGING": str(tmp_path / "shm")}
+    procs, logs = [], []
+
+    def start(uid, grank, port, extra):
+        env = _local_env(0, 1, port)
+        env.update(genv)
+        env.update({"GLOBAL_UNIQUE_ID": uid, "GLOBAL_RANK": str(grank)})
+        log = tmp_path / f"join_{uid}.log"
+        logs.append(log)
+        argv = common + ["--project", str(tmp_path / f"join_{uid}.pkl"), "--ckpt.path", str(tmp_path / f"ck_{uid}"),
+                         "--data.data_rank", str(min(grank, 2)), "--data.data_world_size", "3"] + extra
+        procs.append(_launch(argv, env, log))
+
+    for w in range(2):
+        start(str(w), w, ports[1 + w], [])
+    deadline = time.time() + 240
+    while "step: 4," not in (logs[0].read_text() if logs[0].exists() else ""):      # members are past their first saves
+        assert time.time() < deadline and procs[0].poll() is None, logs[0].read_text()[-3000:]
+        time.sleep(0.5)
+    start("J", 100, ports[3], ["--ckpt.live_recovery_url", "auto"])
+    for p, log in zip(procs, logs):
+        try:
+            rc = p.wait(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise AssertionError(f"timeout; log tail:\n{log.read_text()[-3000:]}")
+        assert rc == 0, f"{log}:\n{log.read_text()[-3000:]}"
+    m0, m1, mj = [pickle.load(open(tmp_path / f"join_{u}.pkl", "rb")) for u in ("0", "1", "J")]
+    outer = lambda m: {x["step"]: x for x in m if "outer_model_hash_outer_step" in x}  # noqa: E731
+    o0, o1, oj = outer(m0), outer(m1), outer(mj)
+    assert oj, "the joiner never took part in an outer step"
+    first = min(oj)
+    assert first > 4 and first % 2 == 0
+    # the joiner ran no inner step before its first outer step ...
+    assert min(x["step"] for x in mj if "Loss" in x) == first + 1
+    # ... and from that outer step on everyone holds the same outer model / momentum and the same inner model
+    for s in sorted(oj):
+        for k in ("outer_model_hash_outer_step", "outer_optimizer_hash_outer_step", "inner_model_hash_outer_step"):
+            assert oj[s][k] == o0[s][k] == o1[s][k], (s, k)
+    peers = {x["step"]: x["num_peers"] for x in m0 if "num_peers" in x}
+    assert peers[first + 1] == 3 and peers[1] == 2
+    assert max(x["step"] for x in mj if "Loss" in x) == total
