@@ -92,7 +92,7 @@ def main():
         else:
             do = torch.randn_like(o)
             dq = torch.empty_like(qkv)
-            ms = timeit(lambda: A.attention_bwd(qkv, o, do, lse, ss, a.heads, a.kv, a.hd, dqkv=dq), a.iters, flush)
+            ms = timeit(lambda: A.attention_bwd(qkv, o, do, lse, ss, a.heads, a.kv, a.hd, dqkv=dq, seq_len=a.seq), a.iters, flush)
             fl *= 2.5
         out.update(shape=[a.batch, a.seq, a.heads, a.kv, a.hd], ms=ms, tflops=fl / ms / 1e9, frac=fl / ms / 1e9 / tf, frac_of=tag)
     elif a.kernel in ("rmsnorm", "rmsnorm_bwd", "swiglu", "swiglu_bwd", "adamw"):

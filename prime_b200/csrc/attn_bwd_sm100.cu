@@ -16,20 +16,12 @@
 // Gradient semantics match autograd through the reference attention
 // (models/llama/model.py:282-302) for scores scaled by `scale`.
 #include "common.cuh"
+#include "attn_bwd.cuh"
+
+#include <cstdlib>
+#include <cstring>
 
 namespace pb {
-
-struct AttnBwdParams {
-    int M, H, KV, n_tiles;
-    const int* seq_start;
-    const float* lse2;     // [H, M]
-    const float* D;        // [H, M]
-    float* dq_acc;         // [M, H*HD] fp32, zero-initialised by the caller
-    __nv_bfloat16* dqkv;   // [M, (H+2KV)*HD]; this kernel writes the k and v column blocks
-    long long dqkv_stride;
-    float scale, scale_log2;
-    int* status;
-};
 
 template <int HD>
 struct AttnBwdCfg {
@@ -121,9 +113,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
 
     // query tiles that can see this kv tile: from the diagonal up to the last tile whose first
     // row's sequence starts at or before the last kv row (seq_start is non-decreasing).
-    int i_hi = kv_tile;
-    while (i_hi + 1 < p.n_tiles && p.seq_start[(i_hi + 1) * 128] <= kv0 + 127) ++i_hi;
-    const int n_q = i_hi - kv_tile + 1;
+    // The warp looks at 32 candidate tiles per step (one load latency per 32 tiles instead of one per tile).
+    int n_q = 1;
+    for (int t0 = kv_tile + 1; t0 < p.n_tiles; t0 += 32) {
+        const int t = t0 + lane;
+        const bool sees = t < p.n_tiles && p.seq_start[t * 128] <= kv0 + 127;
+        const uint32_t m = __ballot_sync(0xffffffffu, sees);
+        const int run = __ffs(~m) - 1;          // leading run of visible tiles (m == all ones: ffs(0) - 1 = -1)
+        if (run >= 0) { n_q += run; break; }
+        n_q += 32;
+    }
     const int n_it = n_q * G;
 
     if (warp < 4) {
@@ -568,13 +567,22 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
 
 }  // namespace pb
 
+static int g_bwd_variant = -1;   // -1: take it from the environment on first use
+// 0 = row-major kernel (default), 1 = persistent transposed-score kernel (head size 64 only)
+extern "C" int pb_attn_bwd_set_variant(int v) {
+    if (v < 0 || v > 1) return -1;
+    g_bwd_variant = v;
+    return 0;
+}
+
 // dq_acc: fp32 [M, H*HD] scratch (zeroed here); D: fp32 [H, M] scratch, computed here from o and dout unless o is
 // null (then the caller has already filled it). Writes all of dqkv.
-// rope_table != null: the inverse rotation is applied to dq and dk on the way out.
+// rope_table != null: the inverse rotation is applied to dq and dk on the way out (position = row % T).
+// tile_scratch: >= ceil(M / 128) + 1 ints of device scratch (head size 64: per-tile spans and the work counter).
 extern "C" int pb_attn_bwd(const void* qkv, const void* o, const void* dout, const float* lse2, const int* seq_start,
                            void* dqkv, float* dq_acc, float* D, const float* rope_table, int T, int M, int H, int KV, int HD,
                            long long qkv_stride, long long o_stride, long long do_stride, long long dqkv_stride, float scale,
-                           int* status, void* stream) {
+                           int* tile_scratch, int* status, void* stream) {
     using namespace pb;
     if (HD != 64 && HD != 128) return -1;
     if (H % KV) return -1;
@@ -604,7 +612,19 @@ extern "C" int pb_attn_bwd(const void* qkv, const void* o, const void* dout, con
     p.M = M; p.H = H; p.KV = KV; p.n_tiles = (M + 127) / 128; p.seq_start = seq_start; p.lse2 = lse2; p.D = D;
     p.dq_acc = dq_acc; p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv); p.dqkv_stride = dqkv_stride;
     p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    rc = HD == 64 ? launch_attn_bwd<64>(tq, tdo, tdq, p, st) : launch_attn_bwd<128>(tq, tdo, tdq, p, st);
+    p.nq = nullptr; p.counter = nullptr; p.n_items = 0;
+    // Head size 64 has a second kernel (attn_bwd_t_sm100.cu: persistent, transposed scores). It is numerically equivalent
+    // and measured slower than this file's kernel (0.65 vs 0.575 ms at 32 x 1024 tokens, 16 heads), so it is opt-in:
+    // PRIME_B200_ATTN_BWD=persistent or pb_attn_bwd_set_variant(1).
+    if (g_bwd_variant < 0) {
+        const char* e = getenv("PRIME_B200_ATTN_BWD");
+        g_bwd_variant = (e && !strcmp(e, "persistent")) ? 1 : 0;
+    }
+    if (HD == 64 && g_bwd_variant == 1) {
+        if (tile_scratch == nullptr) return -3;
+        rc = launch_attn_bwd_t64(tq, tdo, tdq, p, tile_scratch, st);
+    } else if (HD == 64) rc = launch_attn_bwd<64>(tq, tdo, tdq, p, st);
+    else rc = launch_attn_bwd<128>(tq, tdo, tdq, p, st);
     if (rc) return rc;
     const long long total = (long long)M * (H + KV) * (HD / 8);
     long long blocks = (total + 255) / 256;

@@ -19,7 +19,7 @@ from .kernels import _scratch_buf, status_word
 native.register_cuda_sigs({
     "pb_attn_fwd": [native.vp, native.vp, native.vp, native.vp, native.i32, native.i32, native.i32, native.i32,
                     native.i64, native.i64, native.f32, native.vp, native.vp],
-    "pb_attn_bwd": [native.vp] * 9 + [native.i32] * 5 + [native.i64] * 4 + [native.f32, native.vp, native.vp],
+    "pb_attn_bwd": [native.vp] * 9 + [native.i32] * 5 + [native.i64] * 4 + [native.f32, native.vp, native.vp, native.vp],
 })
 
 
@@ -157,8 +157,10 @@ def attention_bwd(qkv: torch.Tensor, o: torch.Tensor, dout: torch.Tensor, lse2: 
         return _small_head_bwd(qkv, dout, seq_start, H, KV, hd, scale, dqkv, rope_table, seq_len)
     dq_acc = _scratch_buf(qkv.device, "attn_dq", M * H * hd)
     D = row_dots if row_dots is not None else _scratch_buf(qkv.device, "attn_D", M * H)
+    tiles = _scratch_buf(qkv.device, "attn_tiles", (M + 127) // 128 + 1, torch.int32)
+    assert rope_table is None or seq_len > 0
     check(native.cuda().pb_attn_bwd(ptr(qkv), ptr(o) if row_dots is None else None, ptr(dout), ptr(lse2), ptr(seq_start), ptr(dqkv), ptr(dq_acc), ptr(D),
-                                    ptr(rope_table), seq_len if rope_table is not None else 1, M, H, KV, hd, qkv.stride(0),
-                                    o.stride(0), dout.stride(0), dqkv.stride(0), scale, ptr(status_word(qkv.device)),
+                                    ptr(rope_table), max(int(seq_len), 1), M, H, KV, hd, qkv.stride(0),
+                                    o.stride(0), dout.stride(0), dqkv.stride(0), scale, ptr(tiles), ptr(status_word(qkv.device)),
                                     stream_ptr()), "pb_attn_bwd")
     return dqkv
