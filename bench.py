@@ -9,6 +9,8 @@ uniform-random tokens, N(0, 0.02) weights.
         --master-port 29511 bench.py --gpus 8 --steps 8 --warmup 3
     python bench.py --impl reference ...        # same step through the reference's own model code
 
+    python bench.py --config {150M,1B-diloco,10B,allreduce} ...   # the other named configurations (benchmarks/bench_configs.py)
+
 Prints ONE JSON line on rank 0. `value` is device-timed (CUDA events around exactly K steps, max over
 ranks) with inputs already resident; `e2e` times the same K steps through the public
 `FusedLlama.train_step` API including the per-step host->device copy of the batch from pinned memory
@@ -83,7 +85,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def dist_setup():
+def dist_setup(cpu_too: bool = False):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -91,8 +93,26 @@ def dist_setup():
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # the other configurations also talk over gloo (the reference's outer step runs on CPU tensors)
+        dist.init_process_group("cpu:gloo,cuda:nccl" if cpu_too else "nccl", device_id=torch.device("cuda", local))
     return world, rank, local
+
+
+def run_other(args, world, rank, local):
+    """1B-diloco / 10B / allreduce: benchmarks/bench_configs.py, with the clock sampler around the whole run."""
+    sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+    import bench_configs as BC
+    table = {("1B-diloco", "ours"): BC.run_1b_diloco_ours, ("1B-diloco", "reference"): BC.run_1b_diloco_reference,
+             ("10B", "ours"): BC.run_10b_ours, ("10B", "reference"): BC.run_10b_reference,
+             ("allreduce", "ours"): BC.run_allreduce_ours, ("allreduce", "reference"): BC.run_allreduce_reference}
+    if args.config == "allreduce" and world < 2:
+        return {"unavailable": "the all-reduce sweep needs at least 2 ranks"} if args.impl == "reference" else \
+            {"metric": "outer-step all-reduce ms", "value": None, "error": "needs at least 2 ranks", "config": {}}
+    sampler = ClockSampler(local)
+    sampler.start()
+    res = table[(args.config, args.impl)](args, world, rank, local)
+    res["clocks"] = sampler.stop()
+    return res
 
 
 def max_over_ranks(ms: float, world: int) -> float:
@@ -174,11 +194,62 @@ def run_ours(args, world, rank, local):
     ms_e2e = max_over_ranks(f0.elapsed_time(f1), world)
     tokens = args.steps * world * PER_GPU_SEQS * SEQ
     h2d = 2 * PER_GPU_SEQS * SEQ * 8
-    return {
+    out = {
         "value": tokens / (ms / 1e3), "ms_per_step": ms / args.steps, "clocks": clocks, "gpu_launches": launches,
-        "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 12},
+        "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 16},
         "final_loss": final_loss, "e2e_final_loss": loss_f,
     }
+    if world > 1:
+        del eng
+        torch.cuda.empty_cache()
+        out["numerics"] = zero_equivalence(comm, world, rank, local)
+    return out
+
+
+def zero_equivalence(comm, world, rank, local):
+    """Outside the timed region: the W-rank sharded engine on a split batch against a single-rank engine on the whole
+    batch (same weights, same data), two optimizer steps of a small Llama. Reports the worst relative error of the fp32
+    master shards, of the gradient norm and of the loss, and whether the bf16 replicas of all ranks are bit-identical."""
+    import torch.distributed as dist
+    from prime_b200.engine.fused_llama import FusedLlama
+    from prime_b200.models.llama import ModelArgs, Transformer
+    margs = ModelArgs(dim=512, n_layers=4, n_heads=8, n_kv_heads=4, ffn_hidden=1536, vocab_size=4096, max_seq_len=256,
+                      init_mode="normal", init_std=0.05)
+    torch.manual_seed(0)
+    model = Transformer(margs)
+    g = torch.Generator().manual_seed(1)
+    per, T = 4, 256
+    B = per * world
+    tok = torch.randint(0, margs.vocab_size, (2, B, T + 1), generator=g)
+    dev = torch.device("cuda", local)
+    sharded = FusedLlama(margs, device=dev, comm=comm, ce_chunk_tokens=1024)
+    sharded.load_from_module(model)
+    single = FusedLlama(margs, device=dev, ce_chunk_tokens=1024)
+    single.load_from_module(model)
+    loss_err = norm_err = 0.0
+    for step in range(2):
+        x, y = tok[step, :, :-1].contiguous(), tok[step, :, 1:].contiguous()
+        l1, n1 = single.train_step(x, y, lr=1e-3, micro_bs=per)
+        lw, nw = sharded.train_step(x[rank * per:(rank + 1) * per], y[rank * per:(rank + 1) * per], lr=1e-3, micro_bs=per)
+        lt = torch.tensor([lw], device="cuda")
+        dist.all_reduce(lt)
+        loss_err = max(loss_err, abs(lt.item() / world - l1) / abs(l1))
+        norm_err = max(norm_err, abs(nw - n1) / n1)
+    worst = 0.0
+    ref = dict(single.named_master_shards())
+    for name, shard in sharded.named_master_shards():
+        seg = sharded.layout.segments[rank][sharded.layout.by_name[name]]
+        r = ref[name][seg.row_start: seg.row_end]
+        if shard.numel():
+            worst = max(worst, ((shard - r).norm() / (r.norm() + 1e-12)).item())
+    mine = sharded.params.view(torch.int16).to(torch.int64).sum()
+    allsum = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(allsum, mine)
+    t = torch.tensor([worst, norm_err, loss_err], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"zero_equiv_max_rel_err": t[0].item(), "grad_norm_rel_err": t[1].item(), "loss_rel_err": t[2].item(),
+            "replicas_bit_identical": all(int(a) == int(allsum[0]) for a in allsum),
+            "how": f"{world}-rank sharded vs 1-rank engine, 2 optimizer steps, small Llama (dim 512, 4 layers), fp32 master shards compared"}
 
 
 def run_reference(args, world, rank, local):
@@ -273,11 +344,19 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro-bs", type=int, default=32)
-    ap.add_argument("--ref-micro-bs", type=int, default=64)  # the reference's own 150M config uses 64 (configs/150M/H100.toml)
+    ap.add_argument("--config", default="150M", choices=["150M", "1B-diloco", "10B", "allreduce"])
+    ap.add_argument("--micro-bs", type=int, default=None)
+    ap.add_argument("--ref-micro-bs", type=int, default=None)
     ap.add_argument("--ce-chunk", type=int, default=32768)
+    ap.add_argument("--per-gpu-seqs", type=int, default=0, help="sequences per GPU and optimizer step (1B-diloco: 8, 10B: 2)")
+    ap.add_argument("--layers", type=int, default=0, help="10B: use only this many blocks (for boxes with fewer than 8 GPUs)")
+    ap.add_argument("--sizes-mb", default="", help="allreduce: comma-separated tensor sizes in MiB")
+    ap.add_argument("--ckpt-dir", default="", help="10B: where the staged checkpoint is persisted (removed afterwards)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.config == "150M":
+        args.micro_bs = args.micro_bs or 32
+        args.ref_micro_bs = args.ref_micro_bs or 64   # the reference's own 150M config uses 64 (configs/150M/H100.toml)
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
     if not torch.cuda.is_available():
         if args.impl == "reference":
@@ -290,9 +369,12 @@ def main():
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr",
                    "127.0.0.1", "--master-port", "29517", os.path.abspath(__file__)] + sys.argv[1:]
             raise SystemExit(subprocess.call(cmd))
-    world, rank, local = dist_setup()
+    world, rank, local = dist_setup(cpu_too=args.config != "150M")
     try:
-        res = run_ours(args, world, rank, local) if args.impl == "ours" else run_reference(args, world, rank, local)
+        if args.config == "150M":
+            res = run_ours(args, world, rank, local) if args.impl == "ours" else run_reference(args, world, rank, local)
+        else:
+            res = run_other(args, world, rank, local)
     except Exception as e:  # noqa: BLE001
         if args.impl == "reference":
             res = {"unavailable": f"reference run failed: {type(e).__name__}: {str(e)[:160]}"}
@@ -301,6 +383,15 @@ def main():
     if rank == 0:
         if "unavailable" in res:
             print(json.dumps({"impl": "reference", "unavailable": res["unavailable"]}))
+        elif args.config != "150M":
+            line = {"metric": res.pop("metric", "tokens/sec"), "value": res.pop("value", None), "unit": res.pop("unit", ""),
+                    "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res.pop("ms_per_step", None),
+                    "higher_is_better": res.pop("higher_is_better", True), "scaling": res.pop("scaling", "weak"), "vs_baseline": None,
+                    "dtype": "bf16" if args.config != "allreduce" else "fp32 payload, uint8 on the wire",
+                    "data": "synthetic uniform-random token ids (seeded), random-init N(0,0.02) weights" if args.config != "allreduce"
+                    else "synthetic N(0, 1e-3) fp32 values (seeded)", "impl": args.impl, "bench_config": args.config}
+            line.update(res)
+            print(json.dumps(line))
         else:
             line = {
                 "metric": "tokens/sec", "value": res["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -314,6 +405,8 @@ def main():
                 "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": res["gpu_launches"], "impl": args.impl,
                 "final_loss": res["final_loss"],
             }
+            if "numerics" in res:
+                line["numerics"] = res["numerics"]
             print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
