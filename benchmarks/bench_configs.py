@@ -144,15 +144,14 @@ def run_allreduce_ours(args, world, rank, local):
             exact = contrib.clone()
             dist.all_reduce(exact)
             y = x.clone()
-            if rank in members:
-                grp.all_reduce_tensor(y, Compression.UINT8, fake=(rank == fake_rank))
-                err = ((y - exact).norm() / exact.norm()).item()
-            else:
-                err = 0.0
+            grp.all_reduce_tensor(y, Compression.UINT8, fake=(rank == fake_rank))      # returns at once on a rank that is not a member
+            err = ((y - exact).norm() / exact.norm()).item() if rank in members else 0.0
             _sync()
             resize[label] = {"participants": len(members), "rel_err": _max_over_ranks(err)}
         grp.set_participants(list(range(world)))
     launches = native.launch_counter()
+    from prime_b200.ops.kernels import check_status
+    check_status()
     big = next((r for r in rows if r["size_mb"] == 1024), rows[-1])
     return {"metric": "outer-step all-reduce ms (uint8 over NVLink, 1 GiB fp32 pseudo-gradient)", "value": big["nvlink_uint8"]["ms"],
             "unit": "ms", "higher_is_better": False, "scaling": "strong", "ms_per_step": big["nvlink_uint8"]["ms"],
@@ -317,7 +316,8 @@ def run_1b_diloco_ours(args, world, rank, local):
                 torch.cuda.synchronize()
                 ts.append((time.perf_counter() - t0) * 1e3)
                 eng.train_step(xd, yd, 3e-4, micro_bs=micro, sync_loss=False)
-            outer[comp] = {"outer_step_ms": _max_over_ranks(ts[-1]), "first_call_ms": _max_over_ranks(ts[0]),
+            phases = {k: _max_over_ranks(v) for k, v in getattr(wgroup, "last_timing_ms", {}).items()}
+            outer[comp] = {"outer_step_ms": _max_over_ranks(ts[-1]), "first_call_ms": _max_over_ranks(ts[0]), "device_phases_ms": phases,
                            "shard_numel": n_shard, "includes": "H2D of outer params + momentum, exchange, Nesterov, D2H, replica refresh"}
             del dl
     check_status()

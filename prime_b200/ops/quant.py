@@ -1,6 +1,6 @@
 """GPU uint8 quantiser primitives (csrc/diloco_comm.cu), usable on their own.
 
-Same scheme as the host quantiser (:mod:`prime_b200.compression`), applied per 1 Mi-element chunk:
+Same scheme as the host quantiser (:mod:`prime_b200.compression`), applied per 32 Ki-element chunk:
 ``uniform_8bit_quantize_cuda(x) -> (q uint8 [n], codebooks fp32 [chunks, 256])`` and
 ``dequantize_cuda(q, codebooks) -> fp32 [n]``. The fused all-reduce uses exactly these kernels for
 its stage A; exposing them lets the error of the wire format be measured in isolation."""
@@ -12,24 +12,20 @@ from .. import native
 from ..native import check, ptr, stream_ptr
 
 native.register_cuda_sigs({
-    "pb_dl_chunk": [], "pb_dl_blocks_per_chunk": [],
-    "pb_dl_stage_a": [native.vp, native.vp, native.i64, native.i32, native.i32, native.vp, native.vp, native.vp, native.vp, native.vp,
-                      native.vp],
+    "pb_dl_chunk": [],
+    "pb_dl_quantize": [native.vp, native.i64, native.vp, native.vp, native.vp],
 })
 
 
 def uniform_8bit_quantize_cuda(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()
     lib = native.cuda()
-    chunk, bpc = lib.pb_dl_chunk(), lib.pb_dl_blocks_per_chunk()
+    chunk = lib.pb_dl_chunk()
     n = x.numel()
     chunks = -(-n // chunk)
     q = torch.empty(n, dtype=torch.uint8, device=x.device)
     lut = torch.empty(chunks, 256, dtype=torch.float32, device=x.device)
-    partial = torch.empty(chunks * bpc, dtype=torch.float32, device=x.device)
-    bsum = torch.empty(chunks * bpc * 256, dtype=torch.int64, device=x.device)
-    bcnt = torch.empty(chunks * bpc * 256, dtype=torch.int32, device=x.device)
-    check(lib.pb_dl_stage_a(ptr(x), None, n, 1, 0, ptr(q), ptr(lut), ptr(partial), ptr(bsum), ptr(bcnt), stream_ptr()), "pb_dl_stage_a")
+    check(lib.pb_dl_quantize(ptr(x), n, ptr(q), ptr(lut), stream_ptr()), "pb_dl_quantize")
     return q, lut
 
 

@@ -18,17 +18,18 @@ import torch.distributed as dist
 from .. import native
 from ..config import Compression
 from ..native import check, ptr, stream_ptr
+from ..ops.kernels import check_status, status_word
 from .symm import SymmComm
 
 native.register_cuda_sigs({
-    "pb_dl_chunk": [], "pb_dl_blocks_per_chunk": [],
-    "pb_dl_stage_a": [native.vp, native.vp, native.i64, native.i32, native.i32, native.vp, native.vp, native.vp, native.vp, native.vp,
-                      native.vp],
-    "pb_dl_stage_b": [native.vp, native.vp, native.vp, native.vp, native.i32, native.i32, native.i64, native.vp, native.vp, native.vp,
-                      native.vp, native.vp],
-    "pb_dl_stage_c": [native.vp, native.vp, native.vp, native.vp, native.i32, native.i32, native.i64, native.vp, native.vp, native.vp,
-                      native.f32, native.f32, native.vp, native.vp],
+    "pb_dl_chunk": [],
+    "pb_dl_allreduce": [native.vp] * 5 + [native.i32, native.i32, C.c_uint, native.i32, native.i32, native.i32, native.i64, native.vp, native.vp,
+                                         native.f32, native.i32, native.vp, native.vp, native.vp, native.f32, native.f32, native.vp, native.vp,
+                                         native.vp, native.i64, native.vp],
+    "pb_get_peer_wait_budget_ns": [],
 })
+
+DL_FLAG_SLOT = 8        # three consecutive slots of the communicator's flag pads: stage A / B / C done
 
 
 class _Work:
@@ -38,20 +39,28 @@ class _Work:
 
 
 class NvlinkWorkerGroup:
+    """See module docstring. Membership of a call is a subset of the communicator's ranks (``set_participants``); it only
+    changes between calls, after a host-side rendezvous of all ranks of the communicator. Every rank of the communicator
+    calls ``all_reduce_tensor`` / ``fused_outer_step`` for every exchange, members or not (a non-member returns at once);
+    that keeps the epoch numbers of the flag protocol in step."""
+
     def __init__(self, comm: SymmComm, max_numel: int):
         self.comm = comm
         self.device = comm.device
         lib = native.cuda()
+        lib.pb_get_peer_wait_budget_ns.restype = C.c_longlong
         self.chunk = lib.pb_dl_chunk()
-        self.bpc = lib.pb_dl_blocks_per_chunk()
         self.capacity = 0
+        self._mask = (1 << comm.world) - 1
+        self._epoch = 0
+        self._prev_epoch = 0
+        self._counters = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._ensure(max_numel)
 
     def _ensure(self, n: int) -> None:
         """(Re)allocate the symmetric exchange buffers for up to ``n`` elements (collective)."""
         if n <= self.capacity:
             return
-        W = self.comm.world
         chunks = -(-n // self.chunk)
         n_pad = chunks * self.chunk
         self.q = self.comm.alloc(n_pad, torch.uint8)
@@ -60,16 +69,29 @@ class NvlinkWorkerGroup:
         self.lut2 = self.comm.alloc(chunks * 256, torch.float32)
         self._pq, self._plut = self.comm.peer_ptrs(self.q), self.comm.peer_ptrs(self.lut)
         self._pq2, self._plut2 = self.comm.peer_ptrs(self.q2), self.comm.peer_ptrs(self.lut2)
-        dev = self.device
-        self.partial = torch.empty(chunks * self.bpc, dtype=torch.float32, device=dev)
-        self.bin_sum = torch.empty(chunks * self.bpc * 256, dtype=torch.int64, device=dev)
-        self.bin_cnt = torch.empty(chunks * self.bpc * 256, dtype=torch.int32, device=dev)
-        self.reduced = torch.empty((-(-chunks // W)) * self.chunk, dtype=torch.float32, device=dev)
         self.capacity = n_pad
+        self._prev_epoch = 0          # fresh buffers after a collective allocation: nothing of an earlier call is being read
+
+    # ---- membership ----
+    def set_participants(self, ranks) -> None:
+        """Active ranks of the following calls. Collective over the communicator (host rendezvous, so no kernel of an
+        earlier call is still running anywhere when the membership changes)."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.comm.group)
+        mask = 0
+        for r in ranks:
+            assert 0 <= r < self.comm.world
+            mask |= 1 << r
+        assert mask, "at least one participant"
+        self._mask = mask
+        self._prev_epoch = 0
+
+    def participants(self) -> list[int]:
+        return [r for r in range(self.comm.world) if (self._mask >> r) & 1]
 
     # ---- process-group-like surface ----
     def size(self) -> int:
-        return self.comm.world
+        return bin(self._mask).count("1")
 
     def rank(self) -> int:
         return self.comm.rank
@@ -79,37 +101,45 @@ class NvlinkWorkerGroup:
         return _Work()
 
     # ---- kernels ----
-    def _exchange(self, a: torch.Tensor, b: torch.Tensor | None, n: int, fake: bool, inv_world: bool):
-        """Stages A and B (+ the barriers around them) for value (a - b) / W, or a / W, or a."""
+    def _run(self, n: int, a, b, scale: float, fake: bool, outer=None, inner=None, mom=None, lr: float = 0.0, mu: float = 0.0, g_out=None):
+        """One exchange (stage A, B, C) for value (a - b) * scale, or a * scale."""
         lib, W, r = native.cuda(), self.comm.world, self.comm.rank
+        self._epoch += 1
+        epoch, prev = self._epoch, self._prev_epoch
+        self._prev_epoch = epoch
+        if not (self._mask >> r) & 1:
+            return False
         assert n <= self.capacity
-        check(lib.pb_dl_stage_a(ptr(a), ptr(b), n, W if inv_world else 1, int(fake), ptr(self.q), ptr(self.lut), ptr(self.partial),
-                                ptr(self.bin_sum), ptr(self.bin_cnt), stream_ptr()), "pb_dl_stage_a")
-        self.comm.barrier(slot=3)
-        check(lib.pb_dl_stage_b(self._pq, self._plut, self._pq2, self._plut2, W, r, n, ptr(self.reduced), ptr(self.partial),
-                                ptr(self.bin_sum), ptr(self.bin_cnt), stream_ptr()), "pb_dl_stage_b")
-        self.comm.barrier(slot=3)
+        check(lib.pb_dl_allreduce(self._pq, self._plut, self._pq2, self._plut2, self.comm._flag_ptrs, W, r, self._mask, epoch, prev,
+                                  DL_FLAG_SLOT, n, ptr(a), ptr(b), scale, int(fake), ptr(outer), ptr(inner), ptr(mom), lr, mu, ptr(g_out),
+                                  ptr(self._counters), ptr(status_word(self.device)), lib.pb_get_peer_wait_budget_ns(), stream_ptr()),
+              "pb_dl_allreduce")
+        return True
 
-    def all_reduce_tensor(self, tensor: torch.Tensor, compression: Compression = Compression.UINT8, average: bool = False) -> None:
-        """In-place all-reduce of a flat fp32 tensor (host or device). ``uint8``: quantised exchange
-        with fp32 accumulation by this package's kernels; ``no``: exact fp32 through the library
-        all-reduce of the group (plain collective, nothing fused with it)."""
+    def all_reduce_tensor(self, tensor: torch.Tensor, compression: Compression = Compression.UINT8, average: bool = False,
+                          fake: bool = False) -> None:
+        """In-place all-reduce of a flat fp32 tensor (host or device) over the active ranks. ``uint8``: quantised exchange
+        with fp32 accumulation by this package's kernels (``fake``: this rank contributes zeros but receives the result);
+        ``no``: exact fp32 through the library all-reduce of the group (plain collective, nothing fused with it)."""
         x = tensor if tensor.is_cuda else tensor.to(self.device, non_blocking=True)
         if compression != Compression.UINT8:
+            assert self._mask == (1 << self.comm.world) - 1, "the library all-reduce runs over the whole communicator"
+            if fake:
+                x.zero_()
             dist.all_reduce(x, group=self.comm.group)
             if average:
                 x.div_(self.comm.world)
         else:
             n = x.numel()
             self._ensure_same(n)
-            self._exchange(x, None, n, fake=False, inv_world=average)
-            lib = native.cuda()
-            check(lib.pb_dl_stage_c(self._pq, self._plut, self._pq2, self._plut2, self.comm.world, self.comm.rank, n, None, None, None,
-                                    0.0, 0.0, ptr(x), stream_ptr()), "pb_dl_stage_c")
-            self.comm.barrier(slot=3)
-            # a peer wait that gave up must fail this reduction (the caller's retry path handles the exception)
-            from ..ops.kernels import check_status
-            check_status(self.device)
+            ran = self._run(n, x, None, 1.0 / self.size() if average else 1.0, fake, g_out=x)
+            if ran and not tensor.is_cuda:
+                # host tensors (the DiLoCo bucket path): the copy back synchronises anyway, so a peer wait that gave up
+                # fails this reduction here (the caller's retry path handles the exception). For device tensors the caller
+                # checks the status word when it synchronises.
+                tensor.copy_(x)
+                check_status(self.device)
+                return None
         if not tensor.is_cuda:
             tensor.copy_(x)
         return None
@@ -132,23 +162,28 @@ class NvlinkWorkerGroup:
             self._outer_dev = outer = torch.empty(n, dtype=torch.float32, device=self.device)
             self._mom_dev = torch.empty(n, dtype=torch.float32, device=self.device)
         mom = self._mom_dev
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ev[0].record()
         outer.copy_(outer_host, non_blocking=True)
         mom.copy_(mom_host, non_blocking=True)
-        lib, W, r = native.cuda(), self.comm.world, self.comm.rank
+        ev[1].record()
         if compression == Compression.UINT8:
-            self._exchange(outer, inner, n, fake=fake, inv_world=True)
-            check(lib.pb_dl_stage_c(self._pq, self._plut, self._pq2, self._plut2, W, r, n, ptr(outer), ptr(inner), ptr(mom), lr, momentum,
-                                    None, stream_ptr()), "pb_dl_stage_c")
-            self.comm.barrier(slot=3)
+            self._run(n, outer, inner, 1.0 / self.size(), fake, outer=outer, inner=inner, mom=mom, lr=lr, mu=momentum)
         else:
+            W = self.comm.world
             g = torch.zeros_like(outer) if fake else (outer - inner)
             dist.all_reduce(g, group=self.comm.group)
             g.div_(W)
             mom.mul_(momentum).add_(g)
             outer.sub_(g.add_(mom, alpha=momentum), alpha=lr)
             inner.copy_(outer)
+        ev[2].record()
         outer_host.copy_(outer, non_blocking=True)
         mom_host.copy_(mom, non_blocking=True)
+        ev[3].record()
         torch.cuda.current_stream().synchronize()
+        # device-timed phases of this outer step: staging in, exchange + Nesterov + inner refresh, staging out
+        self.last_timing_ms = {"h2d": ev[0].elapsed_time(ev[1]), "exchange_update": ev[1].elapsed_time(ev[2]),
+                               "d2h": ev[2].elapsed_time(ev[3])}
         from ..ops.kernels import check_status
         check_status(self.device)

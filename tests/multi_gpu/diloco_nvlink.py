@@ -70,6 +70,30 @@ def main():
     model.master.add_(1e-3 * torch.randn(n, device="cuda"))
     grp.fused_outer_step(model, outer_h, mom_h, lr=0.7, momentum=0.9, fake=(rank == world - 1), compression=Compression.UINT8)
     check_status()
+    # elastic membership, driven from the host between calls: the last rank leaves (it is not part of the next reduction),
+    # then rejoins contributing a zero pseudo-gradient once
+    torch.manual_seed(300 + rank)
+    x = torch.randn(200_003, device="cuda") * 1e-3
+    for members, fake_rank in ((list(range(world - 1)) or [0], None), (list(range(world)), world - 1)):
+        grp.set_participants(members)
+        contrib = x.clone()
+        if rank not in members or rank == fake_rank:
+            contrib.zero_()
+        exact = contrib.clone()
+        dist.all_reduce(exact)
+        got = x.clone()
+        grp.all_reduce_tensor(got, Compression.UINT8, fake=(rank == fake_rank))
+        if rank in members:
+            err = ((got - exact).norm() / exact.norm()).item()
+            if err > 0.06:
+                print(f"[rank {rank}] members {members} fake {fake_rank}: rel err {err:.4f}")
+                ok = False
+        elif not torch.equal(got, x):
+            print(f"[rank {rank}] a rank outside the reduction had its tensor changed")
+            ok = False
+        assert grp.size() == len(members)
+    grp.set_participants(list(range(world)))
+    check_status()
     flag = torch.tensor([0 if ok else 1], device="cuda")
     dist.all_reduce(flag)
     if rank == 0:

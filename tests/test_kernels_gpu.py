@@ -302,7 +302,8 @@ def test_gpu_quantizer_matches_host(n):
     q, lut = uniform_8bit_quantize_cuda(x)
     deq = dequantize_cuda(q, lut)
     assert ((deq - x).norm() / x.norm()).item() < 0.05
-    chunk = 1 << 20
+    from prime_b200 import native
+    chunk = native.cuda().pb_dl_chunk()
     xc = x.cpu()
     for c in range(min(2, lut.shape[0])):
         sl = slice(c * chunk, min(n, (c + 1) * chunk))
