@@ -84,7 +84,7 @@ class LocalComm:
     def peer_ptrs(self, t: torch.Tensor):
         return (C.c_void_p * 1)(t.data_ptr())
 
-    def barrier(self, stream=None):
+    def barrier(self, slot: int = 0, stream=None):
         pass
 
     def host_barrier(self):
@@ -129,6 +129,10 @@ class FusedLlama:
         allsegs = _SegArrays([s for g in range(len(lay.groups)) for s in lay.group_segments(self.rank, g)])
         self._segs_step = [allsegs] if allsegs.n <= max_segs else self._segs
         self._partials = torch.zeros(4096, dtype=torch.float32, device=dev)
+        self._norm_parts = torch.zeros(len(lay.groups), dtype=torch.float32, device=dev)   # sum of squares per group
+        self._reduced_groups: set[int] = set()      # groups whose reduce-scatter is already in flight on the comm stream
+        self.overlap_reduce = True                  # False: every group is reduced after the backward, on the main stream
+        self._reduce_in_backward = False
         self._norm_local = torch.zeros(8, dtype=torch.float32, device=dev)
         self._norm_global = torch.zeros(8, dtype=torch.float32, device=dev)
         self.opt_step = 0
@@ -307,6 +311,8 @@ class FusedLlama:
         self._wgrad(dqkv, xn, self.gqkv[i])
         K.rmsnorm_bwd(x, self.w[pre + "attention_norm.weight"], rstd1, dxn, self.g[pre + "attention_norm.weight"], dres=dh,
                       dx=dx, accumulate_dw=self._accum)
+        if self._reduce_in_backward:
+            self._reduce_group(1 + i, overlapped=True)     # this block's gradients are final: reduce them under the next block's backward
 
     # ------------------------------------------------------------------------------------------
     # full micro-step
@@ -321,6 +327,8 @@ class FusedLlama:
         D, V, L = a.dim, a.vocab_size, a.n_layers
         if seq_start is None:
             seq_start = self.default_seq_start(B, T)
+        self._reduced_groups.clear()
+        self._reduce_in_backward = bool(last_microbatch and self.overlap_reduce and self.device.type == "cuda")
         tok = tokens.reshape(-1)
         lab = labels.reshape(-1)
         xs = [self._buf(f"L{i}.x", (M, D)) for i in range(L + 1)]
@@ -354,6 +362,8 @@ class FusedLlama:
         K.sum_f32(z_rows, out[1:2], scale_ptr=inv[0:1], scale=self.z_weight)
         dx = self._buf("dx_a", (M, D))
         K.rmsnorm_bwd(xs[L], self.w["norm.weight"], rstd, dhn, self.g["norm.weight"], dx=dx, accumulate_dw=self._accum)
+        if self._reduce_in_backward:
+            self._reduce_group(L + 1, overlapped=True)     # head group (final norm + output projection)
         # ---- blocks in reverse ----
         other = self._buf("dx_b", (M, D))
         for i in reversed(range(L)):
@@ -364,6 +374,7 @@ class FusedLlama:
         if not self._accum:
             gE.zero_()
         K.embedding_bwd(tok, dx, gE)
+        self._reduce_in_backward = False
         self._accum = True
         return {"loss": out[0], "z_loss": out[1]}
 
@@ -380,14 +391,17 @@ class FusedLlama:
             return self._optimizer_step_cpu(lr, betas, eps, weight_decay, max_norm)
         lib = native.cuda()
         W = self.world
-        self.comm.barrier()                                   # every rank finished writing its grads
-        for g, sa in enumerate(self._segs_step):
-            if sa.n == 0:
-                continue
-            check(lib.pb_zero_reduce_grads(self._peer_grads, W, self.rank, int(self.grad_dtype == torch.float32), sa.n, sa.full,
-                                           sa.shard, sa.numel, ptr(self.grad_shard), 1.0 / W, ptr(self._partials),
-                                           ptr(self._norm_local), int(g > 0), self._opt_ctas(sa), stream_ptr()),
-                  "pb_zero_reduce_grads")
+        # Reduce-scatter by pull, one launch per parameter group. Groups whose gradients were final during the backward are
+        # already in flight on the comm stream (each behind its own peer barrier); the rest (the embedding, or everything
+        # when the overlap is off) follow now. The sum of squares is kept per group and added up in group order, so the
+        # overlapped and the serial schedule produce the same bits.
+        for g in range(len(self._segs)):
+            if g not in self._reduced_groups:
+                self._reduce_group(g, overlapped=self.overlap_reduce)
+        if self.overlap_reduce:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        self._reduced_groups.clear()
+        K.sum_f32(self._norm_parts, self._norm_local[0:1])
         self.comm.allreduce_scalars(self._norm_local, self._norm_global, 1)   # also orders: all ranks done reading grads
         for g, sa in enumerate(self._segs_step):
             if sa.n == 0:
@@ -399,6 +413,29 @@ class FusedLlama:
         self.comm.barrier()                                   # every rank's replica is complete
         self._accum = False
         return self._norm_global[0].sqrt()
+
+    def _reduce_group(self, g: int, overlapped: bool) -> None:
+        """Reduce-scatter (+ cast / scale + sum of squares) of parameter group ``g``: after a peer barrier that says every
+        rank has written its gradients of the group, pull this rank's slices from all ranks. ``overlapped``: on the comm
+        stream, behind an event of the main stream, so it runs under whatever the main stream does next."""
+        sa = self._segs[g]
+        self._reduced_groups.add(g)
+        lib = native.cuda()
+        main = torch.cuda.current_stream()
+        stream = self.comm_stream if overlapped else main
+        if overlapped:
+            ev = torch.cuda.Event()
+            ev.record(main)
+            stream.wait_event(ev)
+        self.comm.barrier(slot=4, stream=stream)
+        if sa.n == 0:
+            with torch.cuda.stream(stream):
+                self._norm_parts[g:g + 1].zero_()
+            return
+        check(lib.pb_zero_reduce_grads(self._peer_grads, self.world, self.rank, int(self.grad_dtype == torch.float32), sa.n, sa.full,
+                                       sa.shard, sa.numel, ptr(self.grad_shard), 1.0 / self.world, ptr(self._partials),
+                                       ptr(self._norm_parts[g:g + 1]), 0, self._opt_ctas(sa), stream_ptr(stream)),
+              "pb_zero_reduce_grads")
 
     def _opt_ctas(self, sa) -> int:
         """Grid of the reduce and AdamW launches. One merged segment streams best from a grid of one CTA per SM
@@ -449,7 +486,8 @@ class FusedLlama:
             if seq_start is not None:
                 T = tokens.shape[1]
                 ss = seq_start[mb * micro_bs * T: (mb + 1) * micro_bs * T] - mb * micro_bs * T
-            out = self.forward_backward(tokens[sl], labels[sl], seq_start=ss, loss_scale=1.0 / n_micro)
+            out = self.forward_backward(tokens[sl], labels[sl], seq_start=ss, loss_scale=1.0 / n_micro,
+                                        last_microbatch=(mb == n_micro - 1))
             total[0] += out["loss"] / n_micro
             total[1] += out["z_loss"] / n_micro
         norm = self.optimizer_step(lr, betas, eps, weight_decay, max_norm)

@@ -98,6 +98,28 @@ def _recover_from_sidecar_with_retry(ckpt_manager: CkptManager, url: str, limit_
             time.sleep(1.0)
 
 
+def _check_engine_flags(config: Config, fused_path: bool, logger) -> None:
+    """Flags of the reference's FSDP2 / torch.compile stack that mean something else (or nothing) here: say so once
+    instead of accepting them silently."""
+    t = config.train
+    if t.fsdp_cpu_offload:
+        raise ValueError("train.fsdp_cpu_offload is not supported: the engine keeps the sharded fp32 master weights and AdamW "
+                         "moments in HBM (12 bytes per parameter divided by the number of GPUs); only the DiLoCo outer state "
+                         "lives in (pinned) host memory")
+    if not fused_path:
+        return
+    fields = t.model_fields_set
+    if "torch_compile" in fields and t.torch_compile:
+        logger.warning("train.torch_compile has no effect on the GPU path: the model is a fixed schedule of hand-written kernels")
+    if "attn_fn" in fields:
+        logger.warning(f"train.attn_fn={t.attn_fn!r} has no effect on the GPU path: attention always runs the tcgen05 flash "
+                       "kernels (document mask from seq_start)")
+    if "reshard_after_forward" in fields and t.reshard_after_forward:
+        logger.warning("train.reshard_after_forward has no effect: the bf16 parameter replica stays resident on every GPU "
+                       "(2 bytes per parameter) and is refreshed by the sharded AdamW kernel; fp32 master weights, moments "
+                       "and reduced gradients are sharded")
+
+
 def train(config: Config) -> None:
     world_info = get_world_info()
     logger = get_logger(config)
@@ -143,8 +165,10 @@ def train(config: Config) -> None:
     sched = partial(get_scheduler, config.optim.sched_type, num_warmup_steps=config.optim.warmup_steps,
                     num_stable_steps=config.optim.stable_steps, num_training_steps=config.optim.total_steps)
     z_weight = config.optim.z_loss_weight if config.optim.z_loss else None
+    fused_path = use_cuda and config.optim.optim.type == "adam"
+    _check_engine_flags(config, fused_path, logger)
     with sw.record_block("Get Model"):
-        if use_cuda and config.optim.optim.type == "adam":
+        if fused_path:
             from .engine.fused_llama import FusedLlama
             from .ops import kernels as K
             comm = None

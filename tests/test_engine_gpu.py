@@ -97,14 +97,14 @@ class _SilentPeerComm:
     def allreduce_scalars(self, src, dst, n):
         dst[:n].copy_(src[:n])
 
-    def barrier(self, stream=None):
+    def barrier(self, slot=0, stream=None):
         if not self.silent:
             return
         from prime_b200 import native
         from prime_b200.native import check, ptr, stream_ptr
         from prime_b200.ops.kernels import status_word
         self.epoch += 1
-        check(native.cuda().pb_peer_barrier(self._ptrs, 2, 0, 0, self.epoch, ptr(status_word(self.device)), stream_ptr()),
+        check(native.cuda().pb_peer_barrier(self._ptrs, 2, 0, 0, self.epoch, ptr(status_word(self.device)), stream_ptr(stream)),
               "pb_peer_barrier")
 
 

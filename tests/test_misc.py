@@ -300,3 +300,23 @@ def test_wandb_logger_reads_run_name_from_inner_config(monkeypatch):
     from prime_b200.utils.metric_logger import WandbMetricLogger
     WandbMetricLogger(project="p", config={"config": {"run_name": "r1"}, "world_info": {}}, resume=False)
     assert seen["name"] == "r1"
+
+
+def test_engine_flag_checks():
+    """Reference flags that the kernel engine cannot honour are refused or reported, not silently accepted."""
+    import logging
+    from prime_b200.config import Config
+    from prime_b200.train import _check_engine_flags
+    log = logging.getLogger("flagtest")
+    seen = []
+    log.warning = lambda msg, *a: seen.append(msg)
+    base = {"data": {"fake": True}, "name_model": "debugmodel", "type_model": "llama2", "optim": {}}
+    mk = lambda **t: Config(**base, train={"micro_bs": 1, **t})  # noqa: E731
+    with pytest.raises(ValueError, match="fsdp_cpu_offload"):
+        _check_engine_flags(mk(fsdp_cpu_offload=True), True, log)
+    _check_engine_flags(mk(attn_fn="math", torch_compile=True, reshard_after_forward=True), True, log)
+    assert len(seen) == 3
+    seen.clear()
+    _check_engine_flags(mk(), True, log)                    # defaults: nothing to say
+    _check_engine_flags(mk(attn_fn="math"), False, log)     # eager path honours attn_fn
+    assert not seen
