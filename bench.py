@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: training throughput (tokens/s) of Llama-150M (12 x 1024, 16 heads, SwiGLU 4096,
 vocab 32000, seq 1024), bf16 compute with fp32 master weights / AdamW, ZeRO-3-sharded over the GPUs of
-one node, 64 sequences per GPU per optimizer step (global batch 512 at 8 GPUs, weak scaling), synthetic
+one node, 64 sequences per GPU per optimizer step in one micro-batch (global batch 512 at 8 GPUs, weak scaling), synthetic
 uniform-random tokens, N(0, 0.02) weights.
 
     python bench.py --gpus 1 --steps 8 --warmup 3
@@ -355,8 +355,8 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.config == "150M":
-        args.micro_bs = args.micro_bs or 32
-        args.ref_micro_bs = args.ref_micro_bs or 64   # the reference's own 150M config uses 64 (configs/150M/H100.toml)
+        args.micro_bs = args.micro_bs or 64           # both arms: the micro-batch of the reference's own 150M config
+        args.ref_micro_bs = args.ref_micro_bs or 64   # (configs/150M/H100.toml)
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
     if not torch.cuda.is_available():
         if args.impl == "reference":

@@ -141,6 +141,16 @@ class FusedLlama:
         self._rope = K.rope_table(args.max_seq_len * 2, args.head_dim, args.rope_theta, dev)
         self._seq_start_cache: dict[tuple[int, int], torch.Tensor] = {}
         self.comm_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+        # Weight-gradient GEMMs do not feed the input-gradient chain, so they can run on a stream of their own
+        # (PRIME_B200_WGRAD_STREAM=1): the SMs a persistent GEMM leaves idle in its last wave are then open to CTAs of the
+        # other stream's kernel. Hazards are handled per buffer: a wgrad records an event for the tensors it reads, and the
+        # main stream waits for that event before the next kernel that overwrites one of them. Off by default: measured on
+        # the 150M step it changes nothing (109.2-109.4 ms with, 109.1-109.3 ms without) because the step runs against the
+        # 1000 W power cap (SM clock 1.48-1.54 GHz of 1.965), not against idle SMs.
+        import os
+        self.wgrad_stream = torch.cuda.Stream(device=dev) if (dev.type == "cuda" and os.environ.get("PRIME_B200_WGRAD_STREAM", "0") == "1") \
+            else None
+        self._readers: dict[int, torch.cuda.Event] = {}
         # parameter views -----------------------------------------------------------------------
         self.w: dict[str, torch.Tensor] = {}
         self.g: dict[str, torch.Tensor] = {}
@@ -271,7 +281,35 @@ class FusedLlama:
 
     def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, g: torch.Tensor) -> None:
         """g[N,K] (+)= dy[M,N]^T x[M,K]"""
-        K.gemm(dy, x, out=g, residual=g if self._accum else None, a_mn=True, b_mn=True)
+        ws = self.wgrad_stream
+        if ws is None or not dy.is_cuda:
+            K.gemm(dy, x, out=g, residual=g if self._accum else None, a_mn=True, b_mn=True)
+            return
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        ws.wait_event(ready)
+        with torch.cuda.stream(ws):
+            K.gemm(dy, x, out=g, residual=g if self._accum else None, a_mn=True, b_mn=True)
+            done = torch.cuda.Event()
+            done.record(ws)
+        self._readers[dy.data_ptr()] = done
+        self._readers[x.data_ptr()] = done
+
+    def _before_write(self, *tensors: torch.Tensor) -> None:
+        """The main stream is about to overwrite these tensors: wait for weight-gradient GEMMs that still read them."""
+        if not self._readers:
+            return
+        main = torch.cuda.current_stream()
+        for t in tensors:
+            ev = self._readers.pop(t.data_ptr(), None)
+            if ev is not None:
+                main.wait_event(ev)
+
+    def _wait_all_wgrads(self) -> None:
+        if self.wgrad_stream is not None and self._readers:
+            torch.cuda.current_stream().wait_stream(self.wgrad_stream)
+            self._readers.clear()
 
     def _block_bwd(self, i: int, x: torch.Tensor, dout: torch.Tensor, T: int, seq_start: torch.Tensor, dx: torch.Tensor) -> None:
         a = self.args
@@ -279,6 +317,7 @@ class FusedLlama:
         D, F, hd, H, KV = a.dim, a.hidden_dim, a.head_dim, a.n_heads, a.kv_heads
         pre = f"layers.{i}."
         if self._is_ckpt(i):   # recompute the block's activations into the shared workspace
+            self._wait_all_wgrads()    # weight gradients of the block above still read that workspace
             self._block_fwd(i, x, T, seq_start, self._buf("ckpt_out", (M, D)))
         sv = lambda n, shp, dt=torch.bfloat16: self._saved(i, n, shp, dt)  # noqa: E731
         xn, rstd1, qkv, o = sv("xn", (M, D)), sv("rstd1", (M,), torch.float32), sv("qkv", (M, (H + 2 * KV) * hd)), sv("o", (M, H * hd))
@@ -288,12 +327,14 @@ class FusedLlama:
         # out = h + act @ w2^T
         self._wgrad(dout, act, self.g[pre + "feed_forward.w2.weight"])
         # in place: h13 becomes d(h13); d(act) = dout @ w2 stays inside the GEMM whose epilogue does the SwiGLU backward
+        self._before_write(h13)
         K.gemm_dswiglu(dout, self.w[pre + "feed_forward.w2.weight"], h13,
                        dact_ws=None if dout.is_cuda else self._buf("dact", (M, F)))
         dhn = self._buf("dhn", (M, D))
         K.gemm(h13, self.w13[i], out=dhn, b_mn=True)
         self._wgrad(h13, hn, self.g13[i])
         dh = self._buf("dh", (M, D))
+        self._before_write(dh)
         K.rmsnorm_bwd(h, self.w[pre + "ffn_norm.weight"], rstd2, dhn, self.g[pre + "ffn_norm.weight"], dres=dout, dx=dh,
                       accumulate_dw=self._accum)
         # h = x + o @ wo^T
@@ -305,10 +346,12 @@ class FusedLlama:
             dots = None
         self._wgrad(dh, o, self.g[pre + "attention.wo.weight"])
         dqkv = self._buf("dqkv", (M, (H + 2 * KV) * hd))
+        self._before_write(dqkv)
         A.attention_bwd(qkv, o, do, lse2, seq_start, H, KV, hd, dqkv=dqkv, rope_table=self._rope, seq_len=T, row_dots=dots)
         dxn = self._buf("dxn", (M, D))
         K.gemm(dqkv, self.wqkv[i], out=dxn, b_mn=True)
         self._wgrad(dqkv, xn, self.gqkv[i])
+        self._before_write(dx)
         K.rmsnorm_bwd(x, self.w[pre + "attention_norm.weight"], rstd1, dxn, self.g[pre + "attention_norm.weight"], dres=dh,
                       dx=dx, accumulate_dw=self._accum)
         if self._reduce_in_backward:
@@ -327,6 +370,7 @@ class FusedLlama:
         D, V, L = a.dim, a.vocab_size, a.n_layers
         if seq_start is None:
             seq_start = self.default_seq_start(B, T)
+        self._wait_all_wgrads()      # the forward overwrites the saved activations that the last weight gradients read
         self._reduced_groups.clear()
         self._reduce_in_backward = bool(last_microbatch and self.overlap_reduce and self.device.type == "cuda")
         tok = tokens.reshape(-1)
@@ -427,6 +471,8 @@ class FusedLlama:
             ev = torch.cuda.Event()
             ev.record(main)
             stream.wait_event(ev)
+        if self.wgrad_stream is not None:
+            stream.wait_stream(self.wgrad_stream)      # the group's weight gradients are produced there
         self.comm.barrier(slot=4, stream=stream)
         if sa.n == 0:
             with torch.cuda.stream(stream):
