@@ -89,12 +89,17 @@ def dist_setup(cpu_too: bool = False):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
+    host_only = cpu_too == "host"          # CPU ranks only (the reference's all-reduce arm): more ranks than GPUs are fine
+    if not host_only:
+        torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         # the other configurations also talk over gloo (the reference's outer step runs on CPU tensors)
-        dist.init_process_group("cpu:gloo,cuda:nccl" if cpu_too else "nccl", device_id=torch.device("cuda", local))
+        if host_only:
+            dist.init_process_group("gloo")
+        else:
+            dist.init_process_group("cpu:gloo,cuda:nccl" if cpu_too else "nccl", device_id=torch.device("cuda", local))
     return world, rank, local
 
 
@@ -108,6 +113,8 @@ def run_other(args, world, rank, local):
     if args.config == "allreduce" and world < 2:
         return {"unavailable": "the all-reduce sweep needs at least 2 ranks"} if args.impl == "reference" else \
             {"metric": "outer-step all-reduce ms", "value": None, "error": "needs at least 2 ranks", "config": {}}
+    if args.config == "allreduce" and args.impl == "reference":
+        return table[(args.config, args.impl)](args, world, rank, local)       # CPU ranks: no GPU clocks to sample
     sampler = ClockSampler(local)
     sampler.start()
     res = table[(args.config, args.impl)](args, world, rank, local)
@@ -152,7 +159,7 @@ def run_ours(args, world, rank, local):
         from prime_b200.parallel.symm import SymmComm
         comm = SymmComm()
     margs = bench_configs["150M"]
-    eng = FusedLlama(margs, device=torch.device("cuda", local), comm=comm, ce_chunk_tokens=args.ce_chunk)
+    eng = FusedLlama(margs, device=torch.device("cuda", local), comm=comm, ce_chunk_tokens=args.ce_chunk, reshard=args.reshard)
     eng.init_weights(seed=0, std=0.02)
     host = make_batches(args.steps + args.warmup, rank, pinned=True)
     dev = [(x.cuda(non_blocking=True), y.cuda(non_blocking=True)) for x, y in host]
@@ -351,6 +358,7 @@ def main():
     ap.add_argument("--per-gpu-seqs", type=int, default=0, help="sequences per GPU and optimizer step (1B-diloco: 8, 10B: 2)")
     ap.add_argument("--layers", type=int, default=0, help="10B: use only this many blocks (for boxes with fewer than 8 GPUs)")
     ap.add_argument("--sizes-mb", default="", help="allreduce: comma-separated tensor sizes in MiB")
+    ap.add_argument("--reshard", action="store_true", help="150M / 10B: no resident bf16 replica, blocks re-gathered when they run")
     ap.add_argument("--ckpt-dir", default="", help="10B: where the staged checkpoint is persisted (removed afterwards)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -358,7 +366,7 @@ def main():
         args.micro_bs = args.micro_bs or 64           # both arms: the micro-batch of the reference's own 150M config
         args.ref_micro_bs = args.ref_micro_bs or 64   # (configs/150M/H100.toml)
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
-    if not torch.cuda.is_available():
+    if not torch.cuda.is_available() and not (args.config == "allreduce" and args.impl == "reference"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "no CUDA device"}))
         else:
@@ -369,7 +377,8 @@ def main():
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr",
                    "127.0.0.1", "--master-port", "29517", os.path.abspath(__file__)] + sys.argv[1:]
             raise SystemExit(subprocess.call(cmd))
-    world, rank, local = dist_setup(cpu_too=args.config != "150M")
+    host_arm = args.config == "allreduce" and args.impl == "reference"
+    world, rank, local = dist_setup(cpu_too="host" if host_arm else args.config != "150M")
     try:
         if args.config == "150M":
             res = run_ours(args, world, rank, local) if args.impl == "ours" else run_reference(args, world, rank, local)
@@ -399,7 +408,7 @@ def main():
                 "vs_baseline": (res["value"] / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None, "dtype": "bf16",
                 "data": "synthetic uniform-random token ids (seeded), random-init N(0,0.02) weights",
                 "config": {"model": "Llama-150M (12L, dim 1024, 16 heads, ffn 4096, vocab 32000)", "global_batch": world * PER_GPU_SEQS,
-                           "seq_len": SEQ, "parallelism": f"zero3-dp{world}",
+                           "seq_len": SEQ, "parallelism": f"zero3-dp{world}" + ("-reshard" if args.reshard and world > 1 else ""),
                            "micro_bs": args.micro_bs if args.impl == "ours" else args.ref_micro_bs,
                            "l2": "per-step working set (tens of GB of activations) far exceeds the 126 MB L2; no explicit flush"},
                 "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": res["gpu_launches"], "impl": args.impl,

@@ -176,7 +176,7 @@ def run_allreduce_reference(args, world, rank, local):
         from zeroband.C.collectives import ring_allreduce as c_ring  # noqa: F401
     except Exception as e:  # noqa: BLE001
         c_ring_err = f"{type(e).__name__}: gloo headers absent" if "gloo" in str(e) or "extension" in str(e) else str(e)[:120]
-    gloo = dist.new_group(backend="gloo")
+    gloo = dist.group.WORLD if dist.get_backend() == "gloo" else dist.new_group(backend="gloo")
     sizes_mb = [1, 4, 16, 64, 256] if not args.sizes_mb else [float(s) for s in args.sizes_mb.split(",")]
     rows = []
     for mb in sizes_mb:
@@ -496,7 +496,7 @@ def run_10b_ours(args, world, rank, local):
         margs = replace(margs, n_layers=args.layers)
     comm = SymmComm() if world > 1 else None
     seq, per_gpu, micro = margs.max_seq_len, args.per_gpu_seqs or 2, 1
-    eng = FusedLlama(margs, device=dev, comm=comm, ac_ckpt=True)
+    eng = FusedLlama(margs, device=dev, comm=comm, ac_ckpt=True, reshard=getattr(args, "reshard", False))
     eng.init_weights(seed=0, std=0.02)
     g = torch.Generator().manual_seed(1234 + rank)
     tok = torch.randint(0, margs.vocab_size, (per_gpu, seq + 1), generator=g)
@@ -540,8 +540,13 @@ def run_10b_ours(args, world, rank, local):
     need_gb = eng.master.numel() * 4 * 4 * world / 2 ** 30 * 1.15       # master + two moments + outer momentum, all ranks
     free_gb = _shm_free_gb()
     ckpt_dir = args.ckpt_dir or "/tmp/prime_b200_bench_ckpt"
+    import shutil
+    os.makedirs(ckpt_dir, exist_ok=True)
+    disk_gb = shutil.disk_usage(ckpt_dir).free / 2 ** 30
     if free_gb < need_gb:
         ckpt["skipped"] = f"/dev/shm has {free_gb:.0f} GB free, the staged checkpoint needs about {need_gb:.0f} GB"
+    elif disk_gb < need_gb:
+        ckpt["skipped"] = f"{ckpt_dir} has {disk_gb:.0f} GB free, the persisted checkpoint needs about {need_gb:.0f} GB"
     else:
         opt_cfg = AdamConfig()
         backend = FusedBackend(eng, opt_cfg, lambda o: get_scheduler("cosine", o, 10, 100, 1000), mesh=None if world == 1 else _local_mesh(world))
@@ -574,8 +579,8 @@ def run_10b_ours(args, world, rank, local):
             "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * per_gpu * seq * 8, "d2h_bytes_per_step": 16},
             "vs_published_8xH100": tokens / (ms / 1e3) / 46.0e3 if (world == 8 and not args.layers) else None,
             "config": {"model": f"INTELLECT-1 10B shape ({margs.n_layers}L, dim 4096, 32 heads / 8 KV, ffn 14336, vocab 128256)",
-                       "global_batch": world * per_gpu, "seq_len": seq, "parallelism": f"zero3-dp{world}", "micro_bs": micro,
-                       "activation_checkpointing": True, "l2": "per-step working set far exceeds the 126 MB L2; no explicit flush"}}
+                       "global_batch": world * per_gpu, "seq_len": seq, "parallelism": f"zero3-dp{world}" + ("-reshard" if getattr(args, "reshard", False) and world > 1 else ""),
+                       "micro_bs": micro, "activation_checkpointing": True, "l2": "per-step working set far exceeds the 126 MB L2; no explicit flush"}}
 
 
 class _NoData:

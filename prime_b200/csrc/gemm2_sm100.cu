@@ -138,12 +138,20 @@ __device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
 // NVLink exactly once. No multicast, no library call on peer memory.
 constexpr int GATHER_ROWS = 32;
 constexpr int GATHER_MAX_RANKS = 16;
+constexpr int GATHER_MAX_PARTS = 4;
 struct GatherParams {
     int world, rank;
-    const __nv_bfloat16* shard[GATHER_MAX_RANKS];   // rank r's rows [r*rows_per_rank, ...) of B, row pitch ld
+    // B is the row-wise concatenation of n_parts matrices (e.g. wq | wk | wv), each row-sharded over the ranks on its own:
+    // rows [part_begin[p], part_begin[p + 1]) belong to part p, rank r owns rows_per_rank[p] consecutive rows of it starting
+    // at r * rows_per_rank[p], and keeps them at shard[r] + part_off[p] (row pitch ld)
+    const __nv_bfloat16* shard[GATHER_MAX_RANKS];
+    int n_parts;
+    int part_begin[GATHER_MAX_PARTS + 1];
+    int rows_per_rank[GATHER_MAX_PARTS];
+    long long part_off[GATHER_MAX_PARTS];
+    int unit_rot;                                   // gather order: sub-unit (i + unit_rot) mod n_units is the i-th to be fetched
     __nv_bfloat16* full;                            // local [N, ld] buffer the TMA map of B points at
     long long ld;
-    int rows_per_rank;
     int* counters;                                  // [ceil(N/256)] monotonically increasing sub-unit counts
     int target;                                     // counter value that means "n-block complete" for this launch
 };
@@ -211,6 +219,8 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
+        unsigned long long gathered_mask = 0ull;           // all-gather GEMM: n-blocks already seen complete
+        (void)gathered_mask;
         for (int item = pair; item < p.num_items && ok; item += n_pairs) {
             const int tile = item % p.num_tiles, slice = item / p.num_tiles;
             const int kb0 = slice * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
@@ -220,20 +230,25 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
             // my half of the B rows; with the SwiGLU epilogue the halves are the gate rows and the matching up rows
             const int n0 = EPI == GEMM_EPI_SWIGLU ? tn * 128 + int(rank) * p.epi_i0 : tn * G2_BN + int(rank) * 128;
             if constexpr (GATHER) {
-                // wait until every row of this n-block has landed in the local B buffer
-                const int* ctr = g.counters + tn;
-                const uint64_t t0 = globaltimer_ns();
-                while (ok && ld_acquire_gpu(ctr) < g.target) {
-                    if (*abort_flag) ok = false;
-                    else if (globaltimer_ns() - t0 > PB_WAIT_BUDGET_NS) {
-                        *abort_flag = 1;
-                        if (p.status) atomicCAS(p.status, 0, PB_ERR_TIMEOUT_PEER | (int(blockIdx.x) << 8));
-                        ok = false;
+                // wait until every row of this n-block has landed in the local B buffer; an n-block seen complete once is
+                // not polled again (the counters only grow)
+                const bool known = tn < 64 && ((gathered_mask >> tn) & 1ull);
+                if (!known) {
+                    const int* ctr = g.counters + tn;
+                    const uint64_t t0 = globaltimer_ns();
+                    while (ok && ld_acquire_gpu(ctr) < g.target) {
+                        if (*abort_flag) ok = false;
+                        else if (globaltimer_ns() - t0 > PB_WAIT_BUDGET_NS) {
+                            *abort_flag = 1;
+                            if (p.status) atomicCAS(p.status, 0, PB_ERR_TIMEOUT_PEER | (int(blockIdx.x) << 8));
+                            ok = false;
+                        }
                     }
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    fence_proxy_async_global();      // generic-proxy stores of the gather -> async-proxy (TMA) reads
+                    if (tn < 64) gathered_mask |= 1ull << tn;
                 }
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                fence_proxy_async_global();      // generic-proxy stores of the gather -> async-proxy (TMA) reads
             }
             for (int kb = kb0; kb < kb1; ++kb) {
                 ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
@@ -313,11 +328,16 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const int et = threadIdx.x - 64;                       // 0..255 within the eight epilogue warps
             const int n_units = (p.N + GATHER_ROWS - 1) / GATHER_ROWS;
             const int vec_per_row = p.K / 8;                       // 16-byte vectors per row (K % 8 == 0)
-            for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+            for (int u0 = blockIdx.x; u0 < n_units; u0 += gridDim.x) {
+                // rotated by rank: the n-blocks the tiles start with come first, and the ranks do not all pull from one peer
+                const int u = (u0 + g.unit_rot) % n_units;
                 const int r0 = u * GATHER_ROWS, r1 = min(p.N, r0 + GATHER_ROWS);
-                const int owner = r0 / g.rows_per_rank;            // GATHER_ROWS divides rows_per_rank
+                int part = 0;
+                while (part + 1 < g.n_parts && r0 >= g.part_begin[part + 1]) ++part;
+                const int local = r0 - g.part_begin[part];         // GATHER_ROWS divides every part and every rows_per_rank
+                const int owner = local / g.rows_per_rank[part];
                 if (owner != g.rank) {
-                    const __nv_bfloat16* src = g.shard[owner] + (long long)(r0 - owner * g.rows_per_rank) * g.ld;
+                    const __nv_bfloat16* src = g.shard[owner] + g.part_off[part] + (long long)(local - owner * g.rows_per_rank[part]) * g.ld;
                     __nv_bfloat16* dst = g.full + (long long)r0 * g.ld;
                     const int total = (r1 - r0) * vec_per_row;
                     for (int i = et; i < total; i += 256 * 4) {    // 4 independent 16-byte peer loads in flight per thread
@@ -659,7 +679,13 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
     p.tiles_n = EPI == GEMM_EPI_SWIGLU ? p.epi_i0 / 128 : (p.N + G2_BN - 1) / G2_BN;
     p.num_tiles = tiles_m * p.tiles_n;
     p.tiles_m = tiles_m;
-    p.group_m = GATHER ? 1 : tile_band_rows(tiles_m, p.tiles_n, 2ll * p.N * p.K);
+    // with the gather fused in, tiles are numbered in bands of 8 tile rows starting at the n-block the gather fetches first: the
+    // first wave then waits for part of B, not for all of it, while a band's A rows still stay in L2 across its n-blocks
+    // (measured at M32768 N4096 K1024, 2 GPUs: bands of 1 or 8 rows 241 us, 16 rows 247 us, whole columns 278 us)
+    static const int ag_group = [] { const char* e = getenv("PRIME_B200_AG_GROUP_M"); return e ? atoi(e) : 0; }();
+    p.group_m = GATHER ? (ag_group > 0 ? (ag_group < tiles_m ? ag_group : tiles_m) : (tiles_m < 8 ? tiles_m : 8))
+                       : tile_band_rows(tiles_m, p.tiles_n, 2ll * p.N * p.K);
+    p.tn_rot = GATHER ? (g.unit_rot / (G2_BN / GATHER_ROWS)) % p.tiles_n : 0;
     if (p.num_items <= 0) {   // no split-K requested
         p.num_items = p.num_tiles;
         p.kb_per_split = (p.K + BK - 1) / BK;
@@ -755,19 +781,21 @@ extern "C" int pb_gemm_bf16_pair_epi(const void* A, const void* B, void* C, cons
 }
 
 // All-gather fused GEMM: C[M,N] = A[M,K] * B[N,K]^T (+R) where B is row-sharded over `world` ranks.
-//   shards[r]   : rank r's rows [r*rows_per_rank, min(N,(r+1)*rows_per_rank)) of B, pitch ldb (peer pointers)
+//   shards[r]   : base of rank r's shard region (peer pointer); part p of B (part_rows[p] rows, part_rows_per_rank[p] of them
+//                 per rank) sits at shards[r] + part_off[p] elements, row pitch ldb
 //   b_full      : this GPU's [N, ldb] buffer; its own rows must already be in place, the rest is filled here
 //   counters    : int[ceil(N/256)], zeroed once by the caller; `call_index` (1, 2, ...) = number of gathers
 //                 run on these counters including this one (they only grow, so no reset race exists)
 // The caller must order this launch after every rank has published its shard (e.g. SymmComm.barrier()).
-// rows_per_rank must be a multiple of 32.
-extern "C" int pb_gemm_bf16_allgather(const void* A, void* const* shards, void* b_full, void* C, const void* R, int M, int N, int K,
-                                      long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int out_fp32, int world,
-                                      int rank, int rows_per_rank, int* counters, int call_index, int max_ctas, int* status,
-                                      void* stream) {
+// Part sizes and rows per rank must be multiples of 32.
+extern "C" int pb_gemm_bf16_allgather_parts(const void* A, void* const* shards, void* b_full, void* C, const void* R, int M, int N, int K,
+                                            long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int out_fp32, int world,
+                                            int rank, int n_parts, const int* part_rows, const int* part_rows_per_rank,
+                                            const long long* part_off, int* counters, int call_index, int max_ctas, int* status,
+                                            void* stream) {
     using namespace pb;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    if (world > GATHER_MAX_RANKS || (rows_per_rank % GATHER_ROWS) || (K % 8)) return -1;
+    if (world > GATHER_MAX_RANKS || n_parts < 1 || n_parts > GATHER_MAX_PARTS || (K % 8)) return -1;
     if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(b_full) & 15)) return -1;
     const int vec = out_fp32 ? 4 : 8;
     if ((ldc % vec) || (R && (ldr % vec)) || (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(R) & 15)) return -2;
@@ -779,14 +807,42 @@ extern "C" int pb_gemm_bf16_allgather(const void* A, void* const* shards, void* 
     GemmParams p{};
     p.M = M; p.N = N; p.K = K; p.C = C; p.R = R; p.ldc = ldc; p.ldr = ldr; p.out_fp32 = out_fp32; p.status = status;
     GatherParams g{};
-    g.world = world; g.rank = rank; g.full = reinterpret_cast<__nv_bfloat16*>(b_full); g.ld = ldb; g.rows_per_rank = rows_per_rank;
+    g.world = world; g.rank = rank; g.full = reinterpret_cast<__nv_bfloat16*>(b_full); g.ld = ldb;
+    g.n_parts = n_parts;
+    int rows = 0;
+    for (int i = 0; i < n_parts; ++i) {
+        if ((part_rows[i] % GATHER_ROWS) || (part_rows_per_rank[i] % GATHER_ROWS) || part_rows_per_rank[i] <= 0 ||
+            (long long)part_rows_per_rank[i] * world < part_rows[i] || (part_off[i] % 8))
+            return -1;
+        g.part_begin[i] = rows;
+        g.rows_per_rank[i] = part_rows_per_rank[i];
+        g.part_off[i] = part_off[i];
+        rows += part_rows[i];
+    }
+    g.part_begin[n_parts] = rows;
+    if (rows != N) return -1;
     g.counters = counters;
     g.target = call_index * (G2_BN / GATHER_ROWS);     // a partial last n-block still counts its real sub-units below
     for (int r = 0; r < world; ++r) g.shard[r] = reinterpret_cast<const __nv_bfloat16*>(shards[r]);
     if (N % G2_BN) return -3;                          // keep the per-block sub-unit count uniform
+    // start at the n-blocks of this rank's share of the rows: with one part those are its own rows (nothing to fetch),
+    // and in any case the W ranks begin their pulls at W different owners
+    const int tiles_n = N / G2_BN;
+    g.unit_rot = ((tiles_n * rank) / world) * (G2_BN / GATHER_ROWS);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     return a_mn ? launch_gemm_pair<true, false, true>(tmA, tmB, p, max_ctas, st, g)
                 : launch_gemm_pair<false, false, true>(tmA, tmB, p, max_ctas, st, g);
+}
+
+// One part: shards[r] = rank r's rows [r*rows_per_rank, min(N,(r+1)*rows_per_rank)) of B, pitch ldb (peer pointers).
+extern "C" int pb_gemm_bf16_allgather(const void* A, void* const* shards, void* b_full, void* C, const void* R, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int out_fp32, int world,
+                                      int rank, int rows_per_rank, int* counters, int call_index, int max_ctas, int* status,
+                                      void* stream) {
+    const int rows[1] = {N}, rpr[1] = {rows_per_rank};
+    const long long off[1] = {0};
+    return pb_gemm_bf16_allgather_parts(A, shards, b_full, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, out_fp32, world, rank, 1, rows, rpr, off,
+                                        counters, call_index, max_ctas, status, stream);
 }
 
 // Split-K form for products with few output tiles and a long K (weight gradients): `slices` K ranges per

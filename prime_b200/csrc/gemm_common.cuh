@@ -19,6 +19,7 @@ struct GemmParams {
     int num_tiles, tiles_n;
     // CTA-pair kernel: tiles are numbered in bands of group_m tile rows (see gemm_tile_mn); tiles_m = rows of tiles
     int tiles_m, group_m;
+    int tn_rot;      // tile columns are visited starting at this one (all-gather GEMM: the n-block fetched first)
     // split-K: work item w = slice * num_tiles + tile; slice s covers k-blocks [s * kb_per_split, ...) and
     // stores its fp32 partial tile at C + s * split_stride elements (plain direct-store epilogue only)
     int num_items, kb_per_split;
@@ -39,6 +40,7 @@ __device__ __forceinline__ void gemm_tile_mn(const GemmParams& p, int tile, int&
     if (p.group_m <= 1) {
         tm = tile / p.tiles_n;
         tn = tile % p.tiles_n;
+        if (p.tn_rot) tn = (tn + p.tn_rot) % p.tiles_n;
         return;
     }
     const int band = p.group_m * p.tiles_n;
@@ -48,6 +50,7 @@ __device__ __forceinline__ void gemm_tile_mn(const GemmParams& p, int tile, int&
     const int r = tile - g * band;
     tm = first + r % rows;
     tn = r / rows;
+    if (p.tn_rot) tn = (tn + p.tn_rot) % p.tiles_n;
 }
 
 // Epilogues fused into the CTA-pair GEMM:

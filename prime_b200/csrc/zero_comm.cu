@@ -288,6 +288,39 @@ __global__ void __launch_bounds__(256) zero_push_params_kernel(PeerTable params,
     }
 }
 
+// Re-gather of a parameter group for the ZeRO-3 mode that does not keep a replica: copy table entries
+// (owner rank, offset in that rank's bf16 shard buffer) -> offset in the local gathered buffer, plain P2P loads.
+struct GatherTable {
+    int n;
+    int owner[MAX_SEGS];
+    long long src_off[MAX_SEGS];
+    long long dst_off[MAX_SEGS];
+    long long numel[MAX_SEGS];
+    int cta_begin[MAX_SEGS + 1];
+};
+__global__ void __launch_bounds__(256) zero_gather_segments_kernel(PeerTable shards, GatherTable t, __nv_bfloat16* __restrict__ dst) {
+    int s = 0;
+    while (s + 1 < t.n && int(blockIdx.x) >= t.cta_begin[s + 1]) ++s;
+    const long long b = blockIdx.x - t.cta_begin[s], nb = t.cta_begin[s + 1] - t.cta_begin[s];
+    if (nb <= 0) return;
+    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(shards.ptr[t.owner[s]]) + t.src_off[s];
+    __nv_bfloat16* out = dst + t.dst_off[s];
+    const long long n = t.numel[s];
+    const bool vec_ok = (t.src_off[s] % 8 == 0) && (t.dst_off[s] % 8 == 0);
+    const long long nvec = vec_ok ? n / 8 : 0;
+    const long long stride = nb * blockDim.x;
+    for (long long i0 = b * blockDim.x + threadIdx.x; i0 < nvec; i0 += 4 * stride) {      // four 16-byte peer loads in flight
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i0 + u * stride < nvec) v[u] = __ldg(reinterpret_cast<const uint4*>(src) + i0 + u * stride);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i0 + u * stride < nvec) reinterpret_cast<uint4*>(out)[i0 + u * stride] = v[u];
+    }
+    for (long long i = nvec * 8 + b * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = src[i];
+}
+
 static PeerTable make_peers(void* const* ptrs, int world, int rank) {
     PeerTable t{};
     t.world = world; t.rank = rank;
@@ -390,6 +423,26 @@ extern "C" int pb_zero_adamw_gather(void* const* peer_params, int world, int ran
     if (sg.cta_begin[nseg] <= 0) return 0;
     zero_adamw_gather_kernel<<<sg.cta_begin[nseg], 256, 0, ST(stream)>>>(make_peers(peer_params, world, rank), sg, master, grad_shard, m, v,
                                                                          lr, beta1, beta2, eps, wd, bc1, bc2, gnorm_sq, max_norm);
+    return cudaGetLastError() == cudaSuccess ? 0 : -30;
+}
+
+// dst[dst_off[i] ..) = rank owner[i]'s shard buffer [src_off[i] ..), numel[i] bf16 elements each.
+extern "C" int pb_zero_gather_segments(void* const* peer_shards, int world, int rank, int nseg, const int* owner, const long long* src_off,
+                                       const long long* dst_off, const long long* numel, void* dst, int ctas, void* stream) {
+    if (world > MAX_RANKS || nseg > MAX_SEGS || nseg < 0) return -1;
+    if (nseg == 0) return 0;
+    GatherTable t{};
+    t.n = nseg;
+    if (ctas < nseg) ctas = nseg;
+    const SegTable sg = make_segs(nseg, src_off, dst_off, numel, ctas);      // only its CTA split is used
+    for (int i = 0; i < nseg; ++i) {
+        if (owner[i] < 0 || owner[i] >= world) return -1;
+        t.owner[i] = owner[i]; t.src_off[i] = src_off[i]; t.dst_off[i] = dst_off[i]; t.numel[i] = numel[i];
+    }
+    for (int i = 0; i <= nseg; ++i) t.cta_begin[i] = sg.cta_begin[i];
+    if (sg.cta_begin[nseg] <= 0) return 0;
+    zero_gather_segments_kernel<<<sg.cta_begin[nseg], 256, 0, ST(stream)>>>(make_peers(peer_shards, world, rank), t,
+                                                                             reinterpret_cast<__nv_bfloat16*>(dst));
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 

@@ -16,9 +16,17 @@ stream, with the ZeRO-3 collectives on a second stream:
             scalar all-reduce for the global norm, then sharded AdamW that pushes the new bf16
             values into every rank's replica (all-gather by push)
 
-The bf16 parameter replica stays resident on every GPU (180 GB HBM makes ZeRO-3's re-gather
+By default the bf16 parameter replica stays resident on every GPU (180 GB HBM makes ZeRO-3's re-gather
 before every use unnecessary); what is sharded is everything fp32: master weights, AdamW moments
 and the reduced gradient.
+
+``reshard=True`` (the reference's ``train.reshard_after_forward``, src/zeroband/train.py:150-168) drops the
+replica: every rank keeps only its bf16 row shards (symmetric memory) and a transformer block's weights
+exist in full only while the block runs, in one of two block-sized buffers. In the forward the fused QKV
+projection gathers its own operand (wq | wk | wv) inside the GEMM (csrc/gemm2_sm100.cu, all-gather fused
+into the first consuming GEMM) while the rest of the NEXT block is fetched on the comm stream; in the
+backward each block is re-gathered one block ahead. Embedding, final norm and head are gathered once per
+optimizer step.
 """
 from __future__ import annotations
 
@@ -48,6 +56,11 @@ native.register_cuda_sigs({
                              native.i32, native.vp, native.f32, native.i32, native.vp],
     "pb_zero_push_params": [native.vp, native.i32, native.i32, native.i32, native.vp, native.vp, native.vp, native.vp,
                             native.i32, native.vp],
+    "pb_zero_gather_segments": [native.vp, native.i32, native.i32, native.i32, native.vp, native.vp, native.vp, native.vp, native.vp,
+                                native.i32, native.vp],
+    "pb_gemm_bf16_allgather_parts": [native.vp, native.vp, native.vp, native.vp, native.vp, native.i32, native.i32, native.i32, native.i64,
+                                     native.i64, native.i64, native.i64, native.i32, native.i32, native.i32, native.i32, native.i32,
+                                     native.vp, native.vp, native.vp, native.vp, native.i32, native.i32, native.vp, native.vp],
 })
 
 
@@ -99,7 +112,7 @@ class FusedLlama:
 
     def __init__(self, args: ModelArgs, device: torch.device | str = "cuda", comm=None, grad_dtype=torch.bfloat16,
                  ac_ckpt: bool | int = False, ce_chunk_tokens: int = 32768, z_mode: int = K.Z_NONE, z_weight: float = 0.0,
-                 comm_ctas: int = 37):
+                 comm_ctas: int = 37, reshard: bool = False):
         self.args = args
         self.device = torch.device(device)
         self.comm = comm if comm is not None else LocalComm()
@@ -112,15 +125,21 @@ class FusedLlama:
         self.comm_ctas = comm_ctas
         lay = self.layout
         dev = self.device
+        # re-gather mode needs peers to gather from; with one rank the "shard" is the whole model
+        self.reshard = bool(reshard) and self.world > 1 and self.device.type == "cuda"
         # flat buffers --------------------------------------------------------------------------
-        self.params = self.comm.alloc(lay.full_numel, torch.bfloat16, dev)       # replica, symmetric
+        if not self.reshard:
+            self.params = self.comm.alloc(lay.full_numel, torch.bfloat16, dev)   # replica, symmetric
+        else:
+            self.params = None
+            self.param_shard = self.comm.alloc(lay.max_shard_numel, torch.bfloat16, dev)    # this rank's bf16 rows, symmetric
         self.grads = self.comm.alloc(lay.full_numel, grad_dtype, dev)             # local grads, symmetric
         n_shard = lay.shard_numel[self.rank]
         self.master = torch.zeros(n_shard, dtype=torch.float32, device=dev)
         self.exp_avg = torch.zeros(n_shard, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n_shard, dtype=torch.float32, device=dev)
         self.grad_shard = torch.zeros(n_shard, dtype=torch.float32, device=dev)
-        self._peer_params = self.comm.peer_ptrs(self.params)
+        self._peer_params = self.comm.peer_ptrs(self.params) if not self.reshard else None
         self._peer_grads = self.comm.peer_ptrs(self.grads)
         self._segs = [_SegArrays(lay.group_segments(self.rank, g)) for g in range(len(lay.groups))]
         max_segs = native.cuda().pb_zero_max_segs() if dev.type == "cuda" else 16
@@ -155,18 +174,145 @@ class FusedLlama:
         self.w: dict[str, torch.Tensor] = {}
         self.g: dict[str, torch.Tensor] = {}
         for p in lay.params:
-            self.w[p.name] = self.params[p.offset: p.offset + p.numel].view(p.shape)
+            if not self.reshard:
+                self.w[p.name] = self.params[p.offset: p.offset + p.numel].view(p.shape)
             self.g[p.name] = self.grads[p.offset: p.offset + p.numel].view(p.shape)
         D, F, hd, H, KV = args.dim, args.hidden_dim, args.head_dim, args.n_heads, args.kv_heads
         self.wqkv, self.gqkv, self.w13, self.g13 = [], [], [], []
         for i in range(args.n_layers):
             q = lay.params[lay.by_name[f"layers.{i}.attention.wq.weight"]]
             n = (H + 2 * KV) * hd * D
-            self.wqkv.append(self.params[q.offset: q.offset + n].view((H + 2 * KV) * hd, D))
+            self.wqkv.append(self.params[q.offset: q.offset + n].view((H + 2 * KV) * hd, D) if not self.reshard else None)
             self.gqkv.append(self.grads[q.offset: q.offset + n].view((H + 2 * KV) * hd, D))
             w1 = lay.params[lay.by_name[f"layers.{i}.feed_forward.w1.weight"]]
-            self.w13.append(self.params[w1.offset: w1.offset + 2 * F * D].view(2 * F, D))
+            self.w13.append(self.params[w1.offset: w1.offset + 2 * F * D].view(2 * F, D) if not self.reshard else None)
             self.g13.append(self.grads[w1.offset: w1.offset + 2 * F * D].view(2 * F, D))
+        if self.reshard:
+            self._init_reshard()
+
+    # ------------------------------------------------------------------------------------------
+    # re-gather mode: block-sized gathered buffers instead of a resident replica
+    # ------------------------------------------------------------------------------------------
+    def _init_reshard(self) -> None:
+        lay, a, dev = self.layout, self.args, self.device
+        L = a.n_layers
+        self._peer_shards = self.comm.peer_ptrs(self.param_shard)
+        blk = max(lay.groups[1 + i].full_end - lay.groups[1 + i].full_start for i in range(L))
+        self._gbuf = [torch.empty(blk, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self._gbuf_holds = [-1, -1]                 # block whose weights a buffer holds (complete or in flight)
+        self._gbuf_whole = [False, False]           # ... including the other ranks' wq | wk | wv rows
+        self._gbuf_ready: list[torch.cuda.Event | None] = [None, None]    # comm-stream event: the buffer's gather is done
+        self._gbuf_free: list[torch.cuda.Event | None] = [None, None]     # main-stream event: the block that used it is done
+        g0, gh = lay.groups[0], lay.groups[L + 1]
+        self._root_off = {0: 0, L + 1: (g0.full_end - g0.full_start + 63) // 64 * 64}
+        self._root_buf = torch.empty(self._root_off[L + 1] + gh.full_end - gh.full_start, dtype=torch.bfloat16, device=dev)
+        self._root_fresh = False                    # embedding / final norm / head hold the current parameters
+        for g in (0, L + 1):
+            for pi in lay.groups[g].params:
+                p = lay.params[pi]
+                o = self._root_off[g] + p.offset - lay.groups[g].full_start
+                self.w[p.name] = self._root_buf[o: o + p.numel].view(p.shape)
+        # copy tables: (owner rank, offset in its shard buffer) -> offset in the gathered buffer
+        H, KV, hd = a.n_heads, a.kv_heads, a.head_dim
+        self._tab_all, self._tab_rest, self._k2 = {}, {}, {}
+        for g in range(len(lay.groups)):
+            rows_all, rows_rest = [], []
+            fused = set()
+            if 1 <= g <= L:
+                names = [f"layers.{g - 1}.attention.{n}.weight" for n in ("wq", "wk", "wv")]
+                parts = [lay.params[lay.by_name[n]] for n in names]
+                rpr = [-(-p.rows // self.world) for p in parts]
+                n_tot = sum(p.rows for p in parts)
+                ok = all(p.rows % self.world == 0 and r % 32 == 0 for p, r in zip(parts, rpr)) and n_tot % 256 == 0 and a.dim % 8 == 0
+                if ok:
+                    fused = {lay.by_name[n] for n in names}
+                    segs = [lay.segments[self.rank][lay.by_name[n]] for n in names]
+                    self._k2[g] = {
+                        "rows": (C.c_int * 3)(*[p.rows for p in parts]), "rpr": (C.c_int * 3)(*rpr),
+                        "off": (C.c_longlong * 3)(*[s_.shard_offset - segs[0].shard_offset for s_ in segs]),
+                        "shards": (C.c_void_p * self.world)(*[pp + segs[0].shard_offset * 2 for pp in self._peer_shards]),
+                        "n": n_tot, "dst_off": parts[0].offset - lay.groups[g].full_start,
+                        "counters": torch.zeros(n_tot // 256, dtype=torch.int32, device=dev), "calls": 0}
+            base = lay.groups[g].full_start
+            for pi in lay.groups[g].params:
+                for r in range(self.world):
+                    sgm = lay.segments[r][pi]
+                    if sgm.numel <= 0:
+                        continue
+                    row = (r, sgm.shard_offset, sgm.full_offset - base, sgm.numel)
+                    rows_all.append(row)
+                    if pi not in fused or r == self.rank:      # the fused QKV GEMM fetches the other ranks' rows itself
+                        rows_rest.append(row)
+            self._tab_all[g] = self._mk_tables(rows_all)
+            self._tab_rest[g] = self._mk_tables(rows_rest)
+
+    @staticmethod
+    def _mk_tables(rows, limit: int = 128):
+        out = []
+        for i in range(0, len(rows), limit):
+            ch = rows[i: i + limit]
+            n = len(ch)
+            out.append((n, (C.c_int * n)(*[r[0] for r in ch]), (C.c_longlong * n)(*[r[1] for r in ch]),
+                        (C.c_longlong * n)(*[r[2] for r in ch]), (C.c_longlong * n)(*[r[3] for r in ch])))
+        return out
+
+    def _gather_into(self, tables, dst: torch.Tensor, stream) -> None:
+        lib = native.cuda()
+        for n, owner, src, dsto, numel in tables:
+            check(lib.pb_zero_gather_segments(self._peer_shards, self.world, self.rank, n, owner, src, dsto, numel, ptr(dst),
+                                              self.comm_ctas * 2, stream_ptr(stream)), "pb_zero_gather_segments")
+
+    def _bind_block(self, i: int, buf: torch.Tensor) -> None:
+        """Point the weight views of block ``i`` at the gathered buffer that holds it."""
+        lay, a = self.layout, self.args
+        base = lay.groups[1 + i].full_start
+        for pi in lay.groups[1 + i].params:
+            p = lay.params[pi]
+            self.w[p.name] = buf[p.offset - base: p.offset - base + p.numel].view(p.shape)
+        D, F, hd, H, KV = a.dim, a.hidden_dim, a.head_dim, a.n_heads, a.kv_heads
+        q = lay.params[lay.by_name[f"layers.{i}.attention.wq.weight"]]
+        self.wqkv[i] = buf[q.offset - base: q.offset - base + (H + 2 * KV) * hd * D].view((H + 2 * KV) * hd, D)
+        w1 = lay.params[lay.by_name[f"layers.{i}.feed_forward.w1.weight"]]
+        self.w13[i] = buf[w1.offset - base: w1.offset - base + 2 * F * D].view(2 * F, D)
+
+    def _fetch_block(self, i: int, whole: bool) -> None:
+        """Start the gather of block ``i`` on the comm stream into the buffer of its parity (a no-op when the buffer still
+        holds the block). ``whole`` = every weight (backward); otherwise everything except the other ranks' wq | wk | wv
+        rows, which the fused QKV projection fetches inside its GEMM."""
+        slot = i % 2
+        if self._gbuf_holds[slot] == i and (not whole or self._gbuf_whole[slot]):
+            return
+        cs = self.comm_stream
+        if self._gbuf_free[slot] is not None:
+            cs.wait_event(self._gbuf_free[slot])        # the block that last used this buffer has finished on the main stream
+        tables = self._tab_all[1 + i] if (whole or (1 + i) not in self._k2) else self._tab_rest[1 + i]
+        self._gather_into(tables, self._gbuf[slot], cs)
+        ev = torch.cuda.Event()
+        ev.record(cs)
+        self._gbuf_ready[slot] = ev
+        self._gbuf_holds[slot] = i
+        self._gbuf_whole[slot] = whole or (1 + i) not in self._k2
+
+    def _use_block(self, i: int) -> None:
+        """Main stream: block ``i``'s gathered weights are about to be read."""
+        slot = i % 2
+        assert self._gbuf_holds[slot] == i
+        torch.cuda.current_stream().wait_event(self._gbuf_ready[slot])
+        self._bind_block(i, self._gbuf[slot])
+
+    def _release_block(self, i: int) -> None:
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self._gbuf_free[i % 2] = ev
+
+    def _ensure_root(self) -> None:
+        if self._root_fresh:
+            return
+        L = self.args.n_layers
+        main = torch.cuda.current_stream()
+        for g in (0, L + 1):
+            self._gather_into(self._tab_all[g], self._root_buf[self._root_off[g]:], main)
+        self._root_fresh = True
 
     # ------------------------------------------------------------------------------------------
     # parameter I/O
@@ -221,6 +367,13 @@ class FusedLlama:
         # apart: meet on the host first so the bounded device barriers below only ever wait for kernel skew
         self.comm.host_barrier()
         self.comm.barrier()
+        if self.reshard:      # no replica: each rank refreshes its own bf16 rows; peers fetch them when a block runs
+            K.cast_to_bf16(self.master, self.param_shard[: self.master.numel()])
+            self._root_fresh = False
+            self._gbuf_holds = [-1, -1]
+            self.comm.barrier()
+            K.check_status(self.device)
+            return
         for g, sa in enumerate(self._segs):
             if sa.n:
                 check(lib.pb_zero_push_params(self._peer_params, self.world, self.rank, sa.n, sa.full, sa.shard, sa.numel,
@@ -256,16 +409,34 @@ class FusedLlama:
     # ------------------------------------------------------------------------------------------
     # forward / backward of one block
     # ------------------------------------------------------------------------------------------
-    def _block_fwd(self, i: int, x: torch.Tensor, T: int, seq_start: torch.Tensor, out: torch.Tensor) -> None:
+    def _block_fwd(self, i: int, x: torch.Tensor, T: int, seq_start: torch.Tensor, out: torch.Tensor, recompute: bool = False) -> None:
         a = self.args
         M = x.shape[0]
         D, F, hd, H, KV = a.dim, a.hidden_dim, a.head_dim, a.n_heads, a.kv_heads
         pre = f"layers.{i}."
+        fetch = self.reshard and not recompute      # a recompute inside the backward finds the block already gathered
+        if fetch:
+            self._fetch_block(i, whole=False)                   # normally started while the previous block ran
+            if i + 1 < a.n_layers:
+                self._fetch_block(i + 1, whole=False)           # the next block arrives under this one's kernels
+            self._use_block(i)
         xn = self._saved(i, "xn", (M, D))
         rstd1 = self._saved(i, "rstd1", (M,), torch.float32)
         K.rmsnorm_fwd(x, self.w[pre + "attention_norm.weight"], a.norm_eps, out=xn, rstd=rstd1)
         qkv = self._saved(i, "qkv", (M, (H + 2 * KV) * hd))
-        K.gemm_rope(xn, self.wqkv[i], qkv, self._rope, T, H + KV, hd)     # rotary embedding in the GEMM epilogue
+        if fetch and not self._gbuf_whole[i % 2]:
+            # all-gather fused into the first consuming GEMM: the other ranks' wq | wk | wv rows are pulled over NVLink by the
+            # GEMM's own epilogue warps while its tensor cores work on the tiles whose rows have landed
+            k2 = self._k2[1 + i]
+            k2["calls"] += 1
+            check(native.cuda().pb_gemm_bf16_allgather_parts(
+                ptr(xn), k2["shards"], ptr(self.wqkv[i]), ptr(qkv), None, M, k2["n"], D, xn.stride(0), D, qkv.stride(0), 0, 0, 0,
+                self.world, self.rank, 3, k2["rows"], k2["rpr"], k2["off"], ptr(k2["counters"]), k2["calls"], 0,
+                ptr(K.status_word(self.device)), stream_ptr()), "pb_gemm_bf16_allgather_parts")
+            self._gbuf_whole[i % 2] = True
+            K.rope_(qkv, self._rope, T, H + KV, hd)
+        else:
+            K.gemm_rope(xn, self.wqkv[i], qkv, self._rope, T, H + KV, hd)     # rotary embedding in the GEMM epilogue
         o = self._saved(i, "o", (M, H * hd))
         _, lse2 = A.attention_fwd(qkv, seq_start, H, KV, hd, out=o)
         self._ws[f"L{i}.lse2" if not self._is_ckpt(i) else "Lshared.lse2"] = lse2
@@ -278,6 +449,8 @@ class FusedLlama:
         act = self._saved(i, "act", (M, F))
         K.gemm_swiglu(hn, self.w13[i], h13, act)                          # SwiGLU in the GEMM epilogue
         K.gemm(act, self.w[pre + "feed_forward.w2.weight"], out=out, residual=h)
+        if fetch:
+            self._release_block(i)
 
     def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, g: torch.Tensor) -> None:
         """g[N,K] (+)= dy[M,N]^T x[M,K]"""
@@ -318,7 +491,7 @@ class FusedLlama:
         pre = f"layers.{i}."
         if self._is_ckpt(i):   # recompute the block's activations into the shared workspace
             self._wait_all_wgrads()    # weight gradients of the block above still read that workspace
-            self._block_fwd(i, x, T, seq_start, self._buf("ckpt_out", (M, D)))
+            self._block_fwd(i, x, T, seq_start, self._buf("ckpt_out", (M, D)), recompute=True)
         sv = lambda n, shp, dt=torch.bfloat16: self._saved(i, n, shp, dt)  # noqa: E731
         xn, rstd1, qkv, o = sv("xn", (M, D)), sv("rstd1", (M,), torch.float32), sv("qkv", (M, (H + 2 * KV) * hd)), sv("o", (M, H * hd))
         lse2 = self._ws[f"L{i}.lse2" if not self._is_ckpt(i) else "Lshared.lse2"]
@@ -371,6 +544,9 @@ class FusedLlama:
         if seq_start is None:
             seq_start = self.default_seq_start(B, T)
         self._wait_all_wgrads()      # the forward overwrites the saved activations that the last weight gradients read
+        if self.reshard:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())    # gathers start after everything before this call
+            self._ensure_root()
         self._reduced_groups.clear()
         self._reduce_in_backward = bool(last_microbatch and self.overlap_reduce and self.device.type == "cuda")
         tok = tokens.reshape(-1)
@@ -411,7 +587,14 @@ class FusedLlama:
         # ---- blocks in reverse ----
         other = self._buf("dx_b", (M, D))
         for i in reversed(range(L)):
+            if self.reshard:       # re-gather, one block ahead of the backward
+                self._fetch_block(i, whole=True)
+                if i > 0:
+                    self._fetch_block(i - 1, whole=True)
+                self._use_block(i)
             self._block_bwd(i, xs[i], dx, T, seq_start, other)
+            if self.reshard:
+                self._release_block(i)
             dx, other = other, dx
         # ---- embedding ----
         gE = self.g["tok_embeddings.weight"]
@@ -447,7 +630,17 @@ class FusedLlama:
         self._reduced_groups.clear()
         K.sum_f32(self._norm_parts, self._norm_local[0:1])
         self.comm.allreduce_scalars(self._norm_local, self._norm_global, 1)   # also orders: all ranks done reading grads
-        for g, sa in enumerate(self._segs_step):
+        if self.reshard:
+            # no replica to refresh: the new bf16 values go to this rank's own rows only (a one-rank "push")
+            n = self.master.numel()
+            one = (C.c_longlong * 1)
+            check(lib.pb_zero_adamw_gather((C.c_void_p * 1)(self.param_shard.data_ptr()), 1, 0, 1, one(0), one(0), one(n), ptr(self.master),
+                                           ptr(self.grad_shard), ptr(self.exp_avg), ptr(self.exp_avg_sq), lr, betas[0], betas[1],
+                                           eps, weight_decay, self.opt_step, ptr(self._norm_global), max_norm,
+                                           min(self.comm_ctas * 4, 1024), stream_ptr()), "pb_zero_adamw_gather")
+            self._root_fresh = False
+            self._gbuf_holds = [-1, -1]
+        for g, sa in enumerate(self._segs_step if not self.reshard else []):
             if sa.n == 0:
                 continue
             check(lib.pb_zero_adamw_gather(self._peer_params, W, self.rank, sa.n, sa.full, sa.shard, sa.numel, ptr(self.master),
@@ -561,6 +754,9 @@ class FusedLlama:
         M = B * T
         if seq_start is None:
             seq_start = self.default_seq_start(B, T)
+        if self.reshard:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            self._ensure_root()
         x = self._buf("L0.x", (M, a.dim))
         K.embedding_fwd(tokens.reshape(-1), self.w["tok_embeddings.weight"], out=x)
         for i in range(a.n_layers):

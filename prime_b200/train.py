@@ -114,10 +114,9 @@ def _check_engine_flags(config: Config, fused_path: bool, logger) -> None:
     if "attn_fn" in fields:
         logger.warning(f"train.attn_fn={t.attn_fn!r} has no effect on the GPU path: attention always runs the tcgen05 flash "
                        "kernels (document mask from seq_start)")
-    if "reshard_after_forward" in fields and t.reshard_after_forward:
-        logger.warning("train.reshard_after_forward has no effect: the bf16 parameter replica stays resident on every GPU "
-                       "(2 bytes per parameter) and is refreshed by the sharded AdamW kernel; fp32 master weights, moments "
-                       "and reduced gradients are sharded")
+    if "reshard_after_forward" not in fields:
+        logger.info("bf16 parameter replica resident on every GPU (set train.reshard_after_forward=true to keep only the row "
+                    "shards and re-gather each block when it runs)")
 
 
 def train(config: Config) -> None:
@@ -177,6 +176,7 @@ def train(config: Config) -> None:
                 comm = SymmComm(elastic_device_mesh.local_pg, device)
             engine = FusedLlama(margs, device=device, comm=comm,
                                 grad_dtype=torch.float32 if config.train.reduce_fp32 else torch.bfloat16,
+                                reshard=("reshard_after_forward" in config.train.model_fields_set and config.train.reshard_after_forward),
                                 ac_ckpt=config.train.ac_ckpt, z_mode=K.Z_LSE if (z_weight and config.train.fused_linear_ce) else
                                 (K.Z_MAX if z_weight else K.Z_NONE), z_weight=z_weight or 0.0)
             torch.manual_seed(42)

@@ -315,7 +315,7 @@ def test_engine_flag_checks():
     with pytest.raises(ValueError, match="fsdp_cpu_offload"):
         _check_engine_flags(mk(fsdp_cpu_offload=True), True, log)
     _check_engine_flags(mk(attn_fn="math", torch_compile=True, reshard_after_forward=True), True, log)
-    assert len(seen) == 3
+    assert len(seen) == 2
     seen.clear()
     _check_engine_flags(mk(), True, log)                    # defaults: nothing to say
     _check_engine_flags(mk(attn_fn="math"), False, log)     # eager path honours attn_fn

@@ -52,11 +52,12 @@ def test_train_two_gpus_matches_one(tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_zero_sharded_step_matches_single_rank(tmp_path):
+@pytest.mark.parametrize("mode", [[], ["--reshard"], ["--reshard", "--ac"]], ids=["replica", "reshard", "reshard-ac"])
+def test_zero_sharded_step_matches_single_rank(tmp_path, mode):
     n = min(torch.cuda.device_count(), 4)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(get_random_available_port()), os.path.join(ROOT, "tests", "multi_gpu", "zero_equivalence.py")]
+           "--master-port", str(get_random_available_port()), os.path.join(ROOT, "tests", "multi_gpu", "zero_equivalence.py")] + mode
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, (r.stdout + r.stderr)[-4000:]
 
