@@ -103,6 +103,50 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return true;
 }
 
+// Work-item ring of a persistent CTA: one producer warp draws item numbers from a global counter and publishes
+// them (-1 = no more work) into ring[k & 3]; every consumer warp (or single consumer thread) takes each entry once.
+// bar_full[4] are initialised with count 1, bar_empty[4] with the number of consumers.
+struct ItemRing {
+    uint32_t bar_full, bar_empty;   // [4] each
+    volatile int* ring;
+    volatile int* abort_flag;
+    int* status;
+    // producer warp (all lanes call): draws the k-th item of this CTA and publishes it; returns it, or -2 on a timeout
+    __device__ __forceinline__ int publish(int k, int* counter, int n_items) {
+        const int slot = k & 3;
+        bool ok = mbar_wait(bar_empty + 8 * slot, ((k >> 2) & 1) ^ 1, abort_flag, status, PB_ERR_TIMEOUT_EMPTY);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return -2;
+        int idx = 0;
+        if ((threadIdx.x & 31) == 0) {
+            idx = atomicAdd(counter, 1);
+            if (idx >= n_items) idx = -1;
+            ring[slot] = idx;
+            mbar_arrive(bar_full + 8 * slot);
+        }
+        return __shfl_sync(0xffffffffu, idx, 0);
+    }
+    // consumer warp (all lanes call): the k-th item of this CTA, or -2 on a timeout
+    __device__ __forceinline__ int take(int k) {
+        const int slot = k & 3;
+        bool ok = mbar_wait(bar_full + 8 * slot, (k >> 2) & 1, abort_flag, status, PB_ERR_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return -2;
+        const int idx = ring[slot];
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) mbar_arrive(bar_empty + 8 * slot);
+        return idx;
+    }
+    // the same for a consumer that is a single thread
+    __device__ __forceinline__ int take_thread(int k) {
+        const int slot = k & 3;
+        if (!mbar_wait(bar_full + 8 * slot, (k >> 2) & 1, abort_flag, status, PB_ERR_TIMEOUT_FULL)) return -2;
+        const int idx = ring[slot];
+        mbar_arrive(bar_empty + 8 * slot);
+        return idx;
+    }
+};
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -90,25 +90,21 @@ def test_attention_long_context_gqa_packed():
     assert torch.equal(o2[3000:], o[3000:])
 
 
-@pytest.mark.parametrize("B,T,H,KV,packed", [(2, 256, 4, 4, False), (1, 512, 4, 2, True), (3, 384, 4, 1, True)])
-def test_attention_bwd_persistent_variant_matches_default(B, T, H, KV, packed):
-    """Head size 64 has an opt-in persistent backward kernel (transposed scores, work items from a global counter);
-    it must produce the same gradients as the default kernel and as the fp32 reference."""
-    from prime_b200 import native
-    native.register_cuda_sigs({"pb_attn_bwd_set_variant": [native.i32]})
-    lib = native.cuda()
-    hd = 64
+@pytest.mark.parametrize("B,T,H,KV,hd,packed", [(4, 1024, 16, 16, 64, False), (6, 768, 8, 2, 64, True), (2, 2048, 16, 2, 128, False),
+                                                (5, 640, 8, 8, 128, True)])
+def test_attention_bwd_more_items_than_sms(B, T, H, KV, hd, packed):
+    """The backward runs one CTA per SM; each draws (kv tile, kv head) items from a counter and carries its barriers,
+    tensor memory and Q/dO ring from item to item. These cases have more items than a B200 has SMs (or, in the last
+    ones, a few per SM), and a second launch re-uses the counter."""
     qkv, ss = _case(B, T, H, KV, hd, packed, seed=7)
     o, lse2 = A.attention_fwd(qkv, ss, H, KV, hd)
     dout = (torch.randn(B * T, H * hd, device="cuda") * 0.5).bfloat16()
-    base = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd).clone()
-    assert lib.pb_attn_bwd_set_variant(1) == 0
-    try:
-        got = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd).clone()
-        torch.cuda.synchronize()
-        ops.check_status()
-    finally:
-        lib.pb_attn_bwd_set_variant(0)
+    got = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd).clone()
+    again = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd).clone()
+    torch.cuda.synchronize()
+    ops.check_status()
     x = qkv.float().requires_grad_(True)
     (gref,) = torch.autograd.grad(A.attention_reference(x, ss, H, KV, hd), x, dout.float())
-    assert _rel(got, gref) < 3e-2 and _rel(got, base) < 2e-2
+    assert _rel(got, gref) < 3e-2
+    # dQ is summed by reduce-adds whose order depends on which CTA drew which item, so two launches agree to rounding
+    assert _rel(again, got) < 1e-3
