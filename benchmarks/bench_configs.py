@@ -304,21 +304,41 @@ def run_1b_diloco_ours(args, world, rank, local):
     ms_e2e = _max_over_ranks(f0.elapsed_time(f1))
     outer = {}
     if wgroup is not None:
-        for comp in ("uint8", "no"):
-            dl = Diloco(DilocoConfig(inner_steps=inner, compression=Compression(comp)), eng, _StaticMesh(wgroup))
+        # outer state resident on the device (the default: the copy back to the pinned host mirrors runs behind the next
+        # inner step) and staged both ways inside the outer step (what a host-offloaded outer optimizer costs)
+        for comp, resident in (("uint8", True), ("no", True), ("uint8", False), ("no", False)):
+            dl = Diloco(DilocoConfig(inner_steps=inner, compression=Compression(comp), outer_state_resident=resident), eng,
+                        _StaticMesh(wgroup))
             for _ in range(2):                      # inner progress, so the pseudo-gradient is not zero
                 eng.train_step(xd, yd, 3e-4, micro_bs=micro, sync_loss=False)
-            ts = []
-            for rep in range(2):                    # first call allocates staging buffers; the second is the number
+            ts, after_all = [], []
+            for rep in range(4):                    # first call allocates buffers and reads the host copies; the last is the number
                 _sync()
                 t0 = time.perf_counter()
-                dl.step(eng, flag=f"{comp}{rep}")
-                torch.cuda.synchronize()
+                dl.step(eng, flag=f"{comp}{int(resident)}{rep}")
+                torch.cuda.current_stream().synchronize()       # not the side stream that refreshes the host mirrors
                 ts.append((time.perf_counter() - t0) * 1e3)
-                eng.train_step(xd, yd, 3e-4, micro_bs=micro, sync_loss=False)
-            phases = {k: _max_over_ranks(v) for k, v in getattr(wgroup, "last_timing_ms", {}).items()}
-            outer[comp] = {"outer_step_ms": _max_over_ranks(ts[-1]), "first_call_ms": _max_over_ranks(ts[0]), "device_phases_ms": phases,
-                           "shard_numel": n_shard, "includes": "H2D of outer params + momentum, exchange, Nesterov, D2H, replica refresh"}
+                # the step that follows, with its loss read: in resident mode that read shares the copy engine with the
+                # refresh of the host mirrors and returns when the refresh is over
+                tw = time.perf_counter()
+                e0.record()
+                eng.train_step(xd, yd, 3e-4, micro_bs=micro, sync_loss=True)
+                e1.record()
+                torch.cuda.current_stream().synchronize()
+                step_after_wall = (time.perf_counter() - tw) * 1e3
+                _sync()
+                step_after = e0.elapsed_time(e1)
+                after_all.append([round(step_after, 1), round(step_after_wall, 1)])
+                dl.wait_host_state()
+            phases = {k: (_max_over_ranks(v) if isinstance(v, float) else v) for k, v in getattr(wgroup, "last_timing_ms", {}).items()}
+            key = comp if resident else comp + "_staged"
+            outer[key] = {"outer_step_ms": _max_over_ranks(ts[-1]), "first_call_ms": _max_over_ranks(ts[0]), "device_phases_ms": phases,
+                          "inner_step_after_ms": _max_over_ranks(step_after), "inner_step_after_wall_ms": _max_over_ranks(step_after_wall),
+                          "inner_step_after_all_reps_device_wall_ms": after_all, "shard_numel": n_shard,
+                          "host_refresh_on_demand_ms": _max_over_ranks(getattr(wgroup, "last_host_refresh_ms", 0.0)) if resident else None,
+                          "includes": ("pseudo-gradient, exchange, Nesterov, inner refresh, replica refresh; the pinned host copies "
+                                       "are written on demand (checkpoint save, live recovery), not per outer step") if resident else
+                                      "H2D of outer params + momentum, exchange, Nesterov, D2H, replica refresh"}
             del dl
     check_status()
     tokens = inner * world * per_gpu * seq

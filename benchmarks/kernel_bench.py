@@ -62,6 +62,7 @@ def main():
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--cols", type=int, default=1024)
+    ap.add_argument("--mb", type=int, default=1024, help="dl_allreduce: fp32 payload in MB")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--torch", action="store_true", help="also time the torch / library op for comparison")
     a = ap.parse_args()
@@ -95,6 +96,25 @@ def main():
             ms = timeit(lambda: A.attention_bwd(qkv, o, do, lse, ss, a.heads, a.kv, a.hd, dqkv=dq, seq_len=a.seq), a.iters, flush)
             fl *= 2.5
         out.update(shape=[a.batch, a.seq, a.heads, a.kv, a.hd], ms=ms, tflops=fl / ms / 1e9, frac=fl / ms / 1e9 / tf, frac_of=tag)
+    elif a.kernel == "dl_allreduce":
+        # the quantised pseudo-gradient all-reduce (stages A, B, C) as a one-rank group: every byte stays on this GPU, so
+        # the time is the kernels' own HBM / shared-memory cost without any link in the way
+        import torch.distributed as dist
+        from prime_b200.config import Compression
+        from prime_b200.parallel.diloco_comm import NvlinkWorkerGroup
+        from prime_b200.parallel.symm import SymmComm
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        torch.cuda.set_device(0)
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        n = a.mb * (1 << 20) // 4
+        grp = NvlinkWorkerGroup(SymmComm(), n)
+        x = torch.randn(n, device=dev) * 1e-3
+        ms = timeit(lambda: grp.all_reduce_tensor(x, Compression.UINT8), a.iters, flush)
+        K.check_status()
+        # HBM bytes per element: read 4, write 1 (A); read 1, write 1 (B, one rank); read 1, write 4 (C) = 12
+        out.update(shape=[n], ms=ms, gbs=12.0 * n / ms / 1e6, frac=12.0 * n / ms / 1e6 / gbs, frac_of=tag)
+        dist.destroy_process_group()
     elif a.kernel in ("rmsnorm", "rmsnorm_bwd", "swiglu", "swiglu_bwd", "adamw"):
         R, Cn = a.rows, a.cols
         if a.kernel == "rmsnorm":

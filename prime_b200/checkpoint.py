@@ -388,6 +388,8 @@ class CkptManager:
             os.makedirs(ckpt_path, exist_ok=True)
             dcp.save(self.states, checkpoint_id=ckpt_path, process_group=self.process_group)
             if self.diloco_offloaded_optimizer is not None:
+                if self.diloco is not None:
+                    self.diloco.wait_host_state()      # the host copy of the outer momentum may still be on its way
                 with open(os.path.join(ckpt_path, f"__{self.world_info.local_rank}_0.pt"), "wb") as f:
                     torch.save({"optimizer": OuterOptimizerWrapper(self.diloco_offloaded_optimizer).state_dict()}, f)
             data_dir = os.path.join(ckpt_path, "data")
@@ -471,6 +473,8 @@ class CkptManager:
             with open(os.path.join(resume_ckpt_path, f"__{world_info.local_rank}_0.pt"), "rb") as f:
                 rank_state = torch.load(f, weights_only=True)     # tensors and plain values only
             OuterOptimizerWrapper(self.diloco_offloaded_optimizer).load_state_dict(rank_state["optimizer"])
+            if self.diloco is not None:
+                self.diloco.mark_host_state_written()
         if not skip_dataloader:
             if self.config.remote_data_load:
                 self.remote_data_load()
@@ -512,6 +516,8 @@ class CkptManager:
         t0 = time.perf_counter()
         src = self.config.live_recovery_rank_src
         self._logger.debug(f"Start receiving ckpt from rank {src}")
+        if self.diloco is not None:
+            self.diloco.wait_host_state()
         jobs, bufs = [], []
         for i, p in enumerate(self.diloco_offloaded_param_list):
             buf = torch.empty_like(p.data)
@@ -527,6 +533,8 @@ class CkptManager:
         self._logger.debug("live recovery progress: offloaded model received 1/5")
         outer = recv_state_dict(global_pg, src, OuterOptimizerWrapper(self.diloco_offloaded_optimizer).state_dict())
         OuterOptimizerWrapper(self.diloco_offloaded_optimizer).load_state_dict(outer)
+        if self.diloco is not None:
+            self.diloco.mark_host_state_written()
         self._logger.debug("live recovery progress: outer optimizer state dict received 2/5")
         self.training_progress.load_state_dict(recv_state_dict(global_pg, src, self.training_progress.state_dict()))
         self._logger.debug("live recovery progress: training progress state dict received 3/5")
@@ -553,6 +561,8 @@ class CkptManager:
             assert self.diloco_offloaded_param_list is not None, "send_ckpt_to_peer is only supported with diloco"
             t0 = time.perf_counter()
             self._logger.debug(f"Start sending ckpt to rank {dest_rank}")
+            if self.diloco is not None:
+                self.diloco.wait_host_state()
             try:
                 jobs = [global_pg.send([p.data.contiguous()], dest_rank, i) for i, p in enumerate(self.diloco_offloaded_param_list)]
                 for j in jobs:

@@ -84,6 +84,10 @@ class DilocoConfig(BaseConfig):
     inner_steps: int
     compression: Compression = Compression.NO
     retry_all_reduce: int = 3
+    # NVLink worker groups only: keep the fp32 outer parameters and momentum resident in device memory between outer
+    # steps. The pinned host copies are then written only when somebody reads them (checkpoint save, live recovery,
+    # the hash log) instead of inside every outer step. False = stage both ways on every outer step.
+    outer_state_resident: bool = True
 
 
 class MemoryProfilerConfig(BaseConfig):

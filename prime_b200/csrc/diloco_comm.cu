@@ -9,7 +9,7 @@
 // Group = the ranks that hold the same parameter shard in the workers; the ACTIVE members of one call are
 // a bit mask (a worker that left is simply not in it, a worker that just joined contributes zeros once).
 // NVSwitch gives uniform all-to-all bandwidth, so instead of a ring the exchange is direct:
-//   stage A (local)   d = (outer - inner) * s   [0 for a "fake" joiner]; per 32 Ki-element chunk, one CTA of 1024 threads,
+//   stage A (local)   d = (outer - inner) * s   [0 for a "fake" joiner]; per 16 Ki-element chunk, one CTA of 512 threads,
 //                     the chunk held in registers from the first read to the last write:
 //                     sigma from the un-centred L2 norm, scale = 6 sigma / 256,
 //                     q = clamp(round(d / scale) + 128), codebook[b] = mean of members of bin b
@@ -33,13 +33,15 @@
 namespace pb {
 
 constexpr int DL_MAX_RANKS = 16;
-constexpr int DL_CHUNK = 32768;           // elements per quantisation chunk = one CTA's register-resident tile
-constexpr int DL_THREADS = 1024;
+constexpr int DL_CHUNK = 16384;           // elements per quantisation chunk = one CTA's register-resident tile
+constexpr int DL_THREADS = 512;           // two CTAs per SM: one loads or waits at a barrier while the other computes
 constexpr int DL_PER_THREAD = DL_CHUNK / DL_THREADS;   // 32
-constexpr int DL_COPIES = 16;             // shared-memory histogram copies (two warps share one: at most 2048 elements each)
+constexpr int DL_TABLE = 256 * 32;        // words of the CTA's shared table: 256 entries x one copy per lane (32 KB)
 // One 32-bit shared-memory atomic per element: an inner bin holds (count << 20) | sum of the 9-bit fixed-point
-// offsets of its members from the bin's lower edge. A copy sees at most 2048 elements, so the count fits 12 bits and the
-// sum (<= 2048 * 512) fits 20; integer sums do not depend on the order of arrival, so codebooks are bit-reproducible.
+// offsets of its members from the bin's lower edge. The histogram has one copy per lane (word bin * 32 + lane), so the 32
+// atomics of a warp instruction always go to 32 different banks and never to the same word, whatever the values are.
+// A copy sees the 512 elements that the threads with that lane number hold, so the count fits 10 bits and the sum
+// (<= 512 * 512) fits 20; integer sums do not depend on the order of arrival, so codebooks are bit-reproducible.
 // The offset resolution (1/512 of a bin width) puts the codebook entries within 1/1024 of a bin width of the exact mean.
 constexpr int DL_FX_BITS = 9;
 constexpr int DL_CNT_SHIFT = 20;
@@ -122,54 +124,90 @@ __device__ __forceinline__ float dl_block_sum(float v) {
 }
 
 // Quantise the CTA's register-resident chunk and write bytes + codebook. Thread t holds 32 / G groups of G
-// consecutive elements: element (k*1024 + t)*G + j sits in v[G*k + j] (G = 4 after the fp32 loads of stage A, G = 16 after
+// consecutive elements: element (k*512 + t)*G + j sits in v[G*k + j] (G = 4 after the fp32 loads of stage A, G = 16 after
 // the byte loads of stage B). `cnt` = valid elements of the chunk.
+// Rounding without the conversion unit: adding 1.5 * 2^23 to |t| < 2^22 leaves round-to-nearest-even(t) in the low
+// mantissa bits of the sum.
+constexpr float DL_MAGIC = 12582912.f;
+constexpr int DL_MAGIC_BITS = 0x4B400000;
+
+template <int G, bool FULL>
+__device__ __forceinline__ void dl_quantize_body(const float (&v)[DL_PER_THREAD], int cnt, uint8_t* __restrict__ q_chunk,
+                                                 bool q_aligned, unsigned* my_bin, long long (&e_sum)[2], unsigned (&e_cnt)[2],
+                                                 float inv_scale) {
+#pragma unroll
+    for (int k = 0; k < DL_PER_THREAD / G; ++k) {
+        const int e0 = (k * DL_THREADS + int(threadIdx.x)) * G;
+        uint32_t w[G / 4];
+#pragma unroll
+        for (int j = 0; j < G / 4; ++j) w[j] = 0u;
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            int qi = 128;                                                 // elements past the end pack as the zero bin
+            if (FULL || e0 + j < cnt) {
+                const float t = v[G * k + j] * inv_scale;
+                const float m = t + DL_MAGIC;
+                qi = __float_as_int(m) - (DL_MAGIC_BITS - 128);           // nearest bin (a tie, one value in ~10^7, goes to the even one);
+                                                                          // far outside the magic range the sign and a large magnitude survive
+                const float d = t - (m - DL_MAGIC);                       // in [-0.5, 0.5] inside the range
+                qi = max(0, min(255, qi));
+                if (unsigned(qi - 1) < 254u) {
+                    // (count 1 << 20) | offset from the bin's lower edge as 9-bit fixed point: one fused multiply-add and one add
+                    const unsigned val = unsigned(__float_as_int(d * float(1 << DL_FX_BITS) + (DL_MAGIC + float(1 << (DL_FX_BITS - 1)))) -
+                                                  (DL_MAGIC_BITS - (1 << DL_CNT_SHIFT)));
+                    atomicAdd(&my_bin[qi << 5], val);
+                } else {
+                    // the two clamping bins take values from an unbounded range: exact 64-bit sums of their own, kept
+                    // per thread (about one element in 400 lands here) and combined once per chunk
+                    const long long fx = __float2ll_rn(fminf(fmaxf(t, -1.0e6f), 1.0e6f) * float(1 << DL_EDGE_FX_BITS));
+                    if (qi) { e_sum[1] += fx; ++e_cnt[1]; }
+                    else { e_sum[0] += fx; ++e_cnt[0]; }
+                }
+            }
+            w[j >> 2] = __funnelshift_r(w[j >> 2], uint32_t(qi), 8);      // bytes enter at the top: after four, element j sits in byte j & 3
+        }
+        if (q_aligned && (FULL || e0 + G - 1 < cnt)) {
+            if (G == 4) *reinterpret_cast<uint32_t*>(q_chunk + e0) = w[0];
+            else *reinterpret_cast<uint4*>(q_chunk + e0) = make_uint4(w[0], w[1 % (G / 4)], w[2 % (G / 4)], w[3 % (G / 4)]);
+        } else {
+            for (int j = 0; j < G && e0 + j < cnt; ++j) q_chunk[e0 + j] = uint8_t(w[j >> 2] >> (8 * (j & 3)));
+        }
+    }
+}
+
 template <int G>
 __device__ __forceinline__ void dl_quantize_chunk(float (&v)[DL_PER_THREAD], long long cnt, uint8_t* __restrict__ q_chunk,
-                                                  float* __restrict__ lut_chunk, bool q_aligned) {
-    __shared__ unsigned s_bin[DL_COPIES][256];
+                                                  float* __restrict__ lut_chunk, bool q_aligned, unsigned* s_bin) {
     __shared__ unsigned long long s_edge_sum[2];
     __shared__ unsigned s_edge_cnt[2];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < DL_PER_THREAD; ++i) ss += v[i] * v[i];
-    for (int i = threadIdx.x; i < DL_COPIES * 256; i += DL_THREADS) (&s_bin[0][0])[i] = 0u;
+    __syncthreads();                                         // the table's previous use (look-ups, last chunk's codebook) is over
+    for (int i = threadIdx.x; i < DL_TABLE; i += DL_THREADS) s_bin[i] = 0u;
     if (threadIdx.x < 2) { s_edge_sum[threadIdx.x] = 0ull; s_edge_cnt[threadIdx.x] = 0u; }
     ss = dl_block_sum(ss);                                   // also orders the zeroing above before the atomics below
     const float sigma = sqrtf(ss / float(cnt > 1 ? cnt - 1 : 1));
     float scale = 6.f * sigma / 256.f;
     if (!(scale > 0.f) || isinf(scale)) scale = 1.f;         // all-zero chunk (e.g. a fake pseudo-gradient)
     const float inv_scale = 1.f / scale;
-    unsigned* my_bin = s_bin[(threadIdx.x >> 6) % DL_COPIES];
+    unsigned* my_bin = s_bin + (threadIdx.x & 31);
+    long long e_sum[2] = {0ll, 0ll};
+    unsigned e_cnt[2] = {0u, 0u};
+    if (cnt == DL_CHUNK) dl_quantize_body<G, true>(v, DL_CHUNK, q_chunk, q_aligned, my_bin, e_sum, e_cnt, inv_scale);
+    else dl_quantize_body<G, false>(v, int(cnt), q_chunk, q_aligned, my_bin, e_sum, e_cnt, inv_scale);
 #pragma unroll
-    for (int k = 0; k < DL_PER_THREAD / G; ++k) {
-        const long long e0 = (long long)(k * DL_THREADS + threadIdx.x) * G;
-        uint32_t w[G / 4];
+    for (int b = 0; b < 2; ++b) {                            // one shared atomic per warp and clamping bin, and only if it has members
+        unsigned c = e_cnt[b];
+        long long sm = e_sum[b];
 #pragma unroll
-        for (int j = 0; j < G / 4; ++j) w[j] = 0u;
-#pragma unroll
-        for (int j = 0; j < G; ++j) {
-            if (e0 + j < cnt) {
-                const float t = v[G * k + j] * inv_scale;
-                int qi = __float2int_rn(roundf(t)) + 128;                 // roundf: half away from zero
-                qi = max(0, min(255, qi));
-                w[j >> 2] |= uint32_t(qi) << (8 * (j & 3));
-                if (qi > 0 && qi < 255) {
-                    const float o = t - (float(qi) - 128.5f);             // offset from the bin's lower edge, in [0, 1]
-                    atomicAdd(&my_bin[qi], (1u << DL_CNT_SHIFT) | unsigned(__float2int_rn(o * float(1 << DL_FX_BITS))));
-                } else {
-                    // the two clamping bins take values from an unbounded range: exact 64-bit sums of their own
-                    const long long fx = __float2ll_rn(fminf(fmaxf(t, -1.0e6f), 1.0e6f) * float(1 << DL_EDGE_FX_BITS));
-                    atomicAdd(&s_edge_sum[qi ? 1 : 0], static_cast<unsigned long long>(fx));
-                    atomicAdd(&s_edge_cnt[qi ? 1 : 0], 1u);
-                }
-            }
+        for (int o = 16; o > 0; o >>= 1) {
+            c += __shfl_xor_sync(0xffffffffu, c, o);
+            sm += __shfl_xor_sync(0xffffffffu, sm, o);
         }
-        if (q_aligned && e0 + G - 1 < cnt) {
-            if (G == 4) *reinterpret_cast<uint32_t*>(q_chunk + e0) = w[0];
-            else *reinterpret_cast<uint4*>(q_chunk + e0) = make_uint4(w[0], w[1 % (G / 4)], w[2 % (G / 4)], w[3 % (G / 4)]);
-        } else {
-            for (int j = 0; j < G && e0 + j < cnt; ++j) q_chunk[e0 + j] = uint8_t(w[j >> 2] >> (8 * (j & 3)));
+        if ((threadIdx.x & 31) == 0 && c) {
+            atomicAdd(&s_edge_sum[b], static_cast<unsigned long long>(sm));
+            atomicAdd(&s_edge_cnt[b], c);
         }
     }
     __syncthreads();
@@ -180,8 +218,8 @@ __device__ __forceinline__ void dl_quantize_chunk(float (&v)[DL_PER_THREAD], lon
             unsigned long long sum = 0;
             unsigned c = 0;
 #pragma unroll
-            for (int cpy = 0; cpy < DL_COPIES; ++cpy) {
-                const unsigned x = s_bin[cpy][b];
+            for (int l = 0; l < 32; ++l) {
+                const unsigned x = s_bin[(b << 5) + ((l + b) & 31)];      // rotated: the 32 bins of a warp read 32 different banks
                 c += x >> DL_CNT_SHIFT;
                 sum += x & ((1u << DL_CNT_SHIFT) - 1u);
             }
@@ -192,18 +230,19 @@ __device__ __forceinline__ void dl_quantize_chunk(float (&v)[DL_PER_THREAD], lon
         }
         lut_chunk[b] = mean;
     }
-    __syncthreads();       // the shared histograms are reused by the CTA's next chunk
+    __syncthreads();       // the shared table is reused by the CTA's next chunk
 }
 
 // ---- stage A: value -> registers -> bytes + codebook ----
 // value = (a - b) * s, or a * s when b is null, or 0 if fake.
-__global__ void __launch_bounds__(DL_THREADS) dl_stage_a_kernel(DlPeers p, const float* __restrict__ a, const float* __restrict__ b, float s,
+__global__ void __launch_bounds__(DL_THREADS, 2) dl_stage_a_kernel(DlPeers p, const float* __restrict__ a, const float* __restrict__ b, float s,
                                                                 int fake, long long n, int epoch, unsigned* counter, int signal) {
     const long long chunks = (n + DL_CHUNK - 1) / DL_CHUNK;
     const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
     uint8_t* q = p.q[p.rank];
     float* lut = p.lut[p.rank];
     const bool q_aligned = (reinterpret_cast<uintptr_t>(q) & 3) == 0;
+    __shared__ unsigned s_tab[DL_TABLE];
     for (long long chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
         const long long lo = chunk * DL_CHUNK;
         const long long cnt = min((long long)DL_CHUNK, n - lo);
@@ -227,7 +266,7 @@ __global__ void __launch_bounds__(DL_THREADS) dl_stage_a_kernel(DlPeers p, const
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[4 * k + j] = x[j] * s;
         }
-        dl_quantize_chunk<4>(v, cnt, q + lo, lut + chunk * 256, q_aligned);
+        dl_quantize_chunk<4>(v, cnt, q + lo, lut + chunk * 256, q_aligned, s_tab);
     }
     if (signal) dl_publish_done(p, p.slot_a, epoch, counter);
 }
@@ -246,9 +285,10 @@ __device__ __forceinline__ int dl_owner(unsigned mask, long long chunk, long lon
 }
 
 // ---- stage B: pull every active rank's bytes for my chunks, dequantise with that rank's codebook, sum, re-quantise ----
-__global__ void __launch_bounds__(DL_THREADS) dl_stage_b_kernel(DlPeers p, long long n, int epoch, int prev_epoch, unsigned* counter,
+__global__ void __launch_bounds__(DL_THREADS, 2) dl_stage_b_kernel(DlPeers p, long long n, int epoch, int prev_epoch, unsigned* counter,
                                                                 int* status, unsigned long long budget_ns) {
-    extern __shared__ float s_lut[];   // [world][256]
+    __shared__ unsigned s_tab[DL_TABLE];   // histogram of the re-quantisation
+    extern __shared__ float s_lut[];       // [world][256]: every active rank's codebook of the current chunk
     const long long chunks = (n + DL_CHUNK - 1) / DL_CHUNK;
     const int m = __popc(p.mask);
     const long long per = (chunks + m - 1) / m;
@@ -260,19 +300,20 @@ __global__ void __launch_bounds__(DL_THREADS) dl_stage_b_kernel(DlPeers p, long 
     ok = dl_wait_peers(p, p.slot_c, prev_epoch, status, budget_ns) && ok;
     uint8_t* q2 = p.q2[p.rank];
     float* lut2 = p.lut2[p.rank];
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.q[0]) & 15) == 0;    // symmetric buffers share their alignment
     for (long long chunk = first + blockIdx.x; ok && chunk < last; chunk += gridDim.x) {
         const long long lo = chunk * DL_CHUNK;
         const long long cnt = min((long long)DL_CHUNK, n - lo);
+        __syncthreads();                   // the previous chunk's look-ups are over
         for (int i = threadIdx.x; i < p.world * 256; i += DL_THREADS) {
             const int r = i >> 8;
             s_lut[i] = ((p.mask >> r) & 1u) ? p.lut[r][chunk * 256 + (i & 255)] : 0.f;
         }
         __syncthreads();
-        // thread t owns the 16-element groups g = k*1024 + t, k = 0..1: one 16-byte load per peer and group
+        // thread t owns the 16-element groups g = k*512 + t, k = 0..1: one 16-byte load per peer and group
         float acc[DL_PER_THREAD];
 #pragma unroll
         for (int i = 0; i < DL_PER_THREAD; ++i) acc[i] = 0.f;
-        const bool vec_ok = (reinterpret_cast<uintptr_t>(p.q[0]) & 15) == 0;    // symmetric buffers share their alignment
         for (int r = 0; r < p.world; ++r) {
             if (!((p.mask >> r) & 1u)) continue;
             const uint8_t* src = p.q[r] + lo;
@@ -293,16 +334,16 @@ __global__ void __launch_bounds__(DL_THREADS) dl_stage_b_kernel(DlPeers p, long 
             }
         }
         // the fp32 sums stay in registers: quantised once more, bytes and codebook into this rank's second buffer
-        dl_quantize_chunk<16>(acc, cnt, q2 + lo, lut2 + chunk * 256, (reinterpret_cast<uintptr_t>(q2) & 15) == 0);
+        dl_quantize_chunk<16>(acc, cnt, q2 + lo, lut2 + chunk * 256, (reinterpret_cast<uintptr_t>(q2) & 15) == 0, s_tab);
     }
     dl_publish_done(p, p.slot_b, epoch, counter);
 }
 
 // ---- stage C: pull the owners' reduced bytes, dequantise, Nesterov outer step, refresh inner (or write g) ----
-__global__ void __launch_bounds__(DL_THREADS) dl_stage_c_kernel(DlPeers p, long long n, float* __restrict__ outer, float* __restrict__ inner,
+__global__ void __launch_bounds__(DL_THREADS, 2) dl_stage_c_kernel(DlPeers p, long long n, float* __restrict__ outer, float* __restrict__ inner,
                                                                 float* __restrict__ mom, float lr, float mu, float* __restrict__ g_out,
                                                                 int epoch, unsigned* counter, int* status, unsigned long long budget_ns) {
-    __shared__ float s_lut[256];
+    __shared__ float s_lut[256];           // the owner's codebook of the current chunk
     const long long chunks = (n + DL_CHUNK - 1) / DL_CHUNK;
     const int m = __popc(p.mask);
     const long long per = (chunks + m - 1) / m;
@@ -370,7 +411,7 @@ static int dl_grid(long long chunks) {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n_sm = 148;
     }
-    const long long cap = n_sm;                // one CTA of 1024 threads per SM (64 registers per thread), looping over its chunks
+    const long long cap = 2LL * n_sm;          // two CTAs of 512 threads per SM (64 registers per thread), each looping over its chunks
     return int(chunks < cap ? (chunks > 0 ? chunks : 1) : cap);
 }
 

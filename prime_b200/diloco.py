@@ -64,7 +64,25 @@ class Diloco:
         if config.compression == Compression.UINT8:
             from . import native
             native.host()   # build / load the native quantiser + ring now rather than at the first outer step
+        self._host_changed = True      # the device copies of the outer state (NVLink worker groups) are older than the host's
         self._init_offloaded_optimizer(model)
+
+    # ------------------------------------------------------------------ host copies of the outer state
+    def wait_host_state(self) -> None:
+        """Call before reading ``param_list_cpu`` / the outer optimizer's state: with ``outer_state_resident`` they are
+        brought up to date with the device copies only now, on demand."""
+        waiter = getattr(self.elastic_device_mesh.global_pg, "wait_host_copies", None)
+        if waiter is not None:
+            waiter()
+
+    def mark_host_state_written(self) -> None:
+        """Call after writing ``param_list_cpu`` or loading the outer optimizer's state (checkpoint load, live
+        recovery): the next outer step reads the host copies again, and the momentum view is rebuilt because
+        ``load_state_dict`` replaces the optimizer's buffers."""
+        self.wait_host_state()
+        self._host_changed = True
+        if hasattr(self, "_momentum"):
+            del self._momentum
 
     # ------------------------------------------------------------------ setup
     @torch.no_grad()
@@ -173,6 +191,8 @@ class Diloco:
     @torch.no_grad()
     def set_outer_from_inner(self, model) -> None:
         """outer := inner (after a checkpoint load or live recovery)."""
+        self.wait_host_state()
+        self._host_changed = True
         if self._engine_layout:
             self.offloaded_data_flat_tensor.copy_(model.master)
             return
@@ -217,8 +237,10 @@ class Diloco:
                 edm.monitored_barrier(flag)
                 fused(model, self.offloaded_data_flat_tensor, self._momentum_flat(), lr=self.config.outer_lr, momentum=0.9,
                       fake=fake, compression=self.config.compression,
-                      first_step=not getattr(self, "_fused_stepped", False))
+                      first_step=not getattr(self, "_fused_stepped", False),
+                      resident=self.config.outer_state_resident, host_changed=self._host_changed)
                 self._fused_stepped = True
+                self._host_changed = False
                 model.publish_params()
                 return
             except Exception as e:  # noqa: BLE001
@@ -227,6 +249,9 @@ class Diloco:
                 fused = getattr(edm.global_pg, "fused_outer_step", None)
                 if fused is None:
                     break
+        # host path: the host copies are the truth again
+        self.wait_host_state()
+        self._host_changed = True
         self.sync_pseudo_gradient(model, fake=fake, flag=flag)
         self.outer_optimizer.step()
         self.sync_inner_model(model)

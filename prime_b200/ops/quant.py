@@ -1,6 +1,6 @@
 """GPU uint8 quantiser primitives (csrc/diloco_comm.cu), usable on their own.
 
-Same scheme as the host quantiser (:mod:`prime_b200.compression`), applied per 32 Ki-element chunk:
+Same scheme as the host quantiser (:mod:`prime_b200.compression`), applied per 16 Ki-element chunk:
 ``uniform_8bit_quantize_cuda(x) -> (q uint8 [n], codebooks fp32 [chunks, 256])`` and
 ``dequantize_cuda(q, codebooks) -> fp32 [n]``. The fused all-reduce uses exactly these kernels for
 its stage A; exposing them lets the error of the wire format be measured in isolation."""

@@ -55,6 +55,8 @@ class NvlinkWorkerGroup:
         self._epoch = 0
         self._prev_epoch = 0
         self._counters = torch.zeros(4, dtype=torch.int32, device=self.device)
+        import threading
+        self._host_lock = threading.Lock()     # the host copies of the outer state: refreshed on demand, possibly from another thread
         self._ensure(max_numel)
 
     def _ensure(self, n: int) -> None:
@@ -150,40 +152,89 @@ class NvlinkWorkerGroup:
 
     @torch.no_grad()
     def fused_outer_step(self, model, outer_host: torch.Tensor, mom_host: torch.Tensor, lr: float, momentum: float, fake: bool,
-                         compression: Compression, first_step: bool = False) -> None:
+                         compression: Compression, first_step: bool = False, resident: bool = False,
+                         host_changed: bool = True) -> None:
         """One DiLoCo outer step for this rank's shard. ``model.master`` (fp32 device shard) is the
         inner state and receives the new outer parameters; ``outer_host`` / ``mom_host`` are the
-        pinned host copies of outer parameters and momentum (updated in place)."""
-        inner = model.master
-        n = inner.numel()
-        self._ensure_same(n)
-        outer = getattr(self, "_outer_dev", None)
-        if outer is None or outer.numel() != n:
-            self._outer_dev = outer = torch.empty(n, dtype=torch.float32, device=self.device)
-            self._mom_dev = torch.empty(n, dtype=torch.float32, device=self.device)
-        mom = self._mom_dev
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-        ev[0].record()
-        outer.copy_(outer_host, non_blocking=True)
-        mom.copy_(mom_host, non_blocking=True)
-        ev[1].record()
-        if compression == Compression.UINT8:
-            self._run(n, outer, inner, 1.0 / self.size(), fake, outer=outer, inner=inner, mom=mom, lr=lr, mu=momentum)
-        else:
-            W = self.comm.world
-            g = torch.zeros_like(outer) if fake else (outer - inner)
-            dist.all_reduce(g, group=self.comm.group)
-            g.div_(W)
-            mom.mul_(momentum).add_(g)
-            outer.sub_(g.add_(mom, alpha=momentum), alpha=lr)
-            inner.copy_(outer)
-        ev[2].record()
-        outer_host.copy_(outer, non_blocking=True)
-        mom_host.copy_(mom, non_blocking=True)
-        ev[3].record()
-        torch.cuda.current_stream().synchronize()
-        # device-timed phases of this outer step: staging in, exchange + Nesterov + inner refresh, staging out
-        self.last_timing_ms = {"h2d": ev[0].elapsed_time(ev[1]), "exchange_update": ev[1].elapsed_time(ev[2]),
-                               "d2h": ev[2].elapsed_time(ev[3])}
-        from ..ops.kernels import check_status
-        check_status(self.device)
+        pinned host copies of outer parameters and momentum.
+
+        ``resident=False``: both are staged to the device, updated and copied back before this returns.
+        ``resident=True``: the device copies are kept from one outer step to the next; they are re-read from the
+        host only when ``host_changed`` says the host copies were written since (checkpoint load, live recovery), and
+        they are copied back only on demand: call :meth:`wait_host_copies` before reading ``outer_host`` / ``mom_host``."""
+        # the lock keeps a reader's on-demand refresh of the host copies (possibly on another thread) out of the step: it
+        # either finishes before the device copies are rewritten or starts after the step, and then copies the new state
+        with self._host_lock:
+            self._refresh_args = None
+            inner = model.master
+            n = inner.numel()
+            self._ensure_same(n)
+            outer = getattr(self, "_outer_dev", None)
+            fresh = outer is None or outer.numel() != n
+            if fresh:
+                self._outer_dev = outer = torch.empty(n, dtype=torch.float32, device=self.device)
+                self._mom_dev = torch.empty(n, dtype=torch.float32, device=self.device)
+            mom = self._mom_dev
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record()
+            staged_in = fresh or host_changed or not resident
+            if staged_in:
+                outer.copy_(outer_host, non_blocking=True)
+                mom.copy_(mom_host, non_blocking=True)
+            ev[1].record()
+            if compression == Compression.UINT8:
+                self._run(n, outer, inner, 1.0 / self.size(), fake, outer=outer, inner=inner, mom=mom, lr=lr, mu=momentum)
+            else:
+                W = self.comm.world
+                g = torch.zeros_like(outer) if fake else (outer - inner)
+                dist.all_reduce(g, group=self.comm.group)
+                g.div_(W)
+                mom.mul_(momentum).add_(g)
+                outer.sub_(g.add_(mom, alpha=momentum), alpha=lr)
+                inner.copy_(outer)
+            ev[2].record()
+            if resident:
+                # no copy back here: wait_host_copies() makes it when somebody is about to read the host copies
+                self._refresh_args = (outer, mom, outer_host, mom_host, ev[2])
+                ev[2].synchronize()
+            else:
+                outer_host.copy_(outer, non_blocking=True)
+                mom_host.copy_(mom, non_blocking=True)
+                ev[3].record()
+                torch.cuda.current_stream().synchronize()
+            # device-timed phases of this outer step: staging in, exchange + Nesterov + inner refresh, staging out
+            self.last_timing_ms = {"h2d": ev[0].elapsed_time(ev[1]) if staged_in else 0.0, "exchange_update": ev[1].elapsed_time(ev[2]),
+                                   "d2h": 0.0 if resident else ev[2].elapsed_time(ev[3]), "resident": bool(resident)}
+            # a peer wait that gave up raises here. The update kernel skips its work in that case, so the device copies
+            # still hold the state from before this step, and _refresh_args (set above) lets the caller's fallback path
+            # bring the host copies up to date from them.
+            check_status(self.device)
+
+    def wait_host_copies(self) -> None:
+        """Resident mode: bring the pinned host copies of the outer state up to date with the device copies, if an outer
+        step has run since they were last written. Called by whoever is about to read them (checkpoint save, live
+        recovery, the hash log) and at the start of the next outer step; an outer step itself never copies back, so
+        neither it nor the inner steps that follow share a copy engine with gigabytes of transfer."""
+        with self._host_lock:
+            args = getattr(self, "_refresh_args", None)
+            if args is None:
+                return
+            self._refresh_args = None
+            outer, mom, outer_host, mom_host, after = args
+            prev = torch.cuda.current_device()
+            torch.cuda.set_device(self.device)          # the caller may be a checkpoint or recovery thread
+            try:
+                if getattr(self, "_d2h_stream", None) is None:
+                    self._d2h_stream = torch.cuda.Stream(device=self.device)
+                start, done = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                self._d2h_stream.wait_event(after)
+                with torch.cuda.stream(self._d2h_stream):
+                    start.record()
+                    outer_host.copy_(outer, non_blocking=True)
+                    mom_host.copy_(mom, non_blocking=True)
+                    done.record()
+                done.synchronize()
+                self.last_host_refresh_ms = start.elapsed_time(done)
+            finally:
+                torch.cuda.set_device(prev)
+

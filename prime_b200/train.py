@@ -51,6 +51,7 @@ def log_hash_training_state(config: Config, backend, diloco: Diloco | None, metr
     logger.debug(f"inner optimizer hash {id} : {inner_opt}")
     metrics = {"step": step, f"inner_model_hash_{id}": inner_model, f"inner_optimizer_hash_{id}": inner_opt}
     if config.diloco is not None and diloco is not None:
+        diloco.wait_host_state()
         outer_opt = utils.get_optimizer_signature(diloco.outer_optimizer)
         outer_model = utils.get_tensor_list_signature([p.data for p in diloco.param_list_cpu])
         logger.debug(f"outer diloco optimizer hash {id} : {outer_opt}")

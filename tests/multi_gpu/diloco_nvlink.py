@@ -70,6 +70,35 @@ def main():
     model.master.add_(1e-3 * torch.randn(n, device="cuda"))
     grp.fused_outer_step(model, outer_h, mom_h, lr=0.7, momentum=0.9, fake=(rank == world - 1), compression=Compression.UINT8)
     check_status()
+    # outer state resident on the device: two steps give the same outer parameters, momentum and inner shard, bit for
+    # bit, as two steps that stage through the host; the host mirrors are valid after wait_host_copies(); a host copy
+    # that was rewritten between steps (checkpoint load) is read again when the caller says so
+    def two_steps(resident):
+        torch.manual_seed(900 + rank)
+        m = _FakeModel((outer0 + 1e-3 * torch.randn(n)).cuda())
+        oh, mh = outer0.clone().pin_memory(), torch.zeros(n).pin_memory()
+        grp._outer_dev = None                                   # start from the host copies
+        for s_ in range(2):
+            grp.fused_outer_step(m, oh, mh, lr=0.7, momentum=0.9, fake=False, compression=Compression.UINT8,
+                                 resident=resident, host_changed=(s_ == 0))
+            m.master.add_(1e-3 * torch.randn(n, device="cuda"))
+        grp.wait_host_copies()
+        return oh.clone(), mh.clone(), m, oh, mh
+    o_st, m_st, _, _, _ = two_steps(False)
+    o_re, m_re, mdl, oh, mh = two_steps(True)
+    if not (torch.equal(o_st, o_re) and torch.equal(m_st, m_re)):
+        print(f"[rank {rank}] resident outer state differs from the staged one")
+        ok = False
+    oh.copy_(outer0)                                            # the host copies are rewritten (as a checkpoint load does)
+    mh.zero_()
+    mdl.master.copy_((outer0 + 1e-3 * (1 + 0.1 * torch.randn(n))).cuda())
+    grp.fused_outer_step(mdl, oh, mh, lr=0.7, momentum=0.9, fake=False, compression=Compression.UINT8, resident=True, host_changed=True)
+    grp.wait_host_copies()
+    want = -0.7 * 1.9 * 1e-3                                     # first Nesterov step from zero momentum: -lr * (1 + mu) * g, g = -1e-3
+    if abs((oh - outer0).mean().item() + want) > 2e-4:
+        print(f"[rank {rank}] rewritten host copies were not read again: mean update {(oh - outer0).mean().item():.6f}")
+        ok = False
+    check_status()
     # elastic membership, driven from the host between calls: the last rank leaves (it is not part of the next reduction),
     # then rejoins contributing a zero pseudo-gradient once
     torch.manual_seed(300 + rank)
