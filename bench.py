@@ -360,6 +360,7 @@ def main():
     ap.add_argument("--sizes-mb", default="", help="allreduce: comma-separated tensor sizes in MiB")
     ap.add_argument("--reshard", action="store_true", help="150M / 10B: no resident bf16 replica, blocks re-gathered when they run")
     ap.add_argument("--ckpt-dir", default="", help="10B: where the staged checkpoint is persisted (removed afterwards)")
+    ap.add_argument("--skip-ckpt", action="store_true", help="10B: leave the checkpoint part out (steps and outer step only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.config == "150M":

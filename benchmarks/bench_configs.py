@@ -548,12 +548,21 @@ def run_10b_ours(args, world, rank, local):
     mesh_pg = types.SimpleNamespace(size=lambda: 1, rank=lambda: 0, barrier=lambda: types.SimpleNamespace(wait=lambda: None),
                                     all_reduce_tensor=lambda t, c, average=False: None)
     dl = Diloco(DilocoConfig(inner_steps=100, compression=Compression.NO), eng, _StaticMesh(mesh_pg))
-    eng.train_step(xd, yd, 7.5e-5, micro_bs=micro, sync_loss=False)
-    _sync()
+    ts = []
+    for rep in range(2):          # the first call allocates the device copies and the pinned momentum mirror
+        eng.train_step(xd, yd, 7.5e-5, micro_bs=micro, sync_loss=False)
+        _sync()
+        t0 = time.perf_counter()
+        dl.step(eng, flag=f"o{rep}")
+        torch.cuda.synchronize()
+        ts.append((time.perf_counter() - t0) * 1e3)
+    outer["outer_step_ms"] = _max_over_ranks(ts[-1])
+    outer["first_call_ms"] = _max_over_ranks(ts[0])
     t0 = time.perf_counter()
-    dl.step(eng, flag="o")
-    torch.cuda.synchronize()
-    outer["host_offload_outer_step_ms"] = _max_over_ranks((time.perf_counter() - t0) * 1e3)
+    dl.wait_host_state()
+    outer["host_refresh_on_demand_ms"] = _max_over_ranks((time.perf_counter() - t0) * 1e3)
+    outer["includes"] = ("one worker, host-side exchange path: pseudo-gradient on the device, device-to-host copy, (no partner: "
+                         "identity all-reduce), copy back, Nesterov on the device copies of the outer state, inner refresh")
     outer["shard_numel"] = eng.master.numel()
     # ---- one asynchronous checkpoint through the staging directory ----
     ckpt = {}
@@ -563,7 +572,9 @@ def run_10b_ours(args, world, rank, local):
     import shutil
     os.makedirs(ckpt_dir, exist_ok=True)
     disk_gb = shutil.disk_usage(ckpt_dir).free / 2 ** 30
-    if free_gb < need_gb:
+    if getattr(args, "skip_ckpt", False):
+        ckpt["skipped"] = "--skip-ckpt"
+    elif free_gb < need_gb:
         ckpt["skipped"] = f"/dev/shm has {free_gb:.0f} GB free, the staged checkpoint needs about {need_gb:.0f} GB"
     elif disk_gb < need_gb:
         ckpt["skipped"] = f"{ckpt_dir} has {disk_gb:.0f} GB free, the persisted checkpoint needs about {need_gb:.0f} GB"

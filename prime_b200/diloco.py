@@ -23,6 +23,7 @@ Design differences from the reference:
 from __future__ import annotations
 
 import re
+import threading
 import time
 
 import torch
@@ -64,13 +65,22 @@ class Diloco:
         if config.compression == Compression.UINT8:
             from . import native
             native.host()   # build / load the native quantiser + ring now rather than at the first outer step
-        self._host_changed = True      # the device copies of the outer state (NVLink worker groups) are older than the host's
+        self._host_changed = True      # the device copies of the outer state are older than the host's
+        self._dev = None               # (outer, momentum, pseudo-gradient) fp32 device copies of this rank's shard, see _device_state
+        self._host_stale = False       # the device copies are newer than the host's (refreshed on demand by wait_host_state)
+        self._state_lock = threading.Lock()
         self._init_offloaded_optimizer(model)
 
     # ------------------------------------------------------------------ host copies of the outer state
     def wait_host_state(self) -> None:
         """Call before reading ``param_list_cpu`` / the outer optimizer's state: with ``outer_state_resident`` they are
         brought up to date with the device copies only now, on demand."""
+        with self._state_lock:
+            if self._host_stale and self._dev is not None:
+                outer, mom, _ = self._dev
+                self.offloaded_data_flat_tensor.copy_(outer)
+                self._momentum_flat().copy_(mom)
+                self._host_stale = False
         waiter = getattr(self.elastic_device_mesh.global_pg, "wait_host_copies", None)
         if waiter is not None:
             waiter()
@@ -79,10 +89,38 @@ class Diloco:
         """Call after writing ``param_list_cpu`` or loading the outer optimizer's state (checkpoint load, live
         recovery): the next outer step reads the host copies again, and the momentum view is rebuilt because
         ``load_state_dict`` replaces the optimizer's buffers."""
-        self.wait_host_state()
-        self._host_changed = True
-        if hasattr(self, "_momentum"):
-            del self._momentum
+        waiter = getattr(self.elastic_device_mesh.global_pg, "wait_host_copies", None)
+        if waiter is not None:
+            waiter()
+        with self._state_lock:
+            self._host_stale = False       # whatever the device held is superseded by what was just written
+            self._host_changed = True
+            if hasattr(self, "_momentum"):
+                del self._momentum
+
+    def _device_state(self, model):
+        """fp32 device copies of outer parameters and momentum plus a pseudo-gradient buffer for this rank's shard, for
+        the fused engine on CUDA with ``outer_state_resident``: the outer step then costs one device-to-host copy of the
+        pseudo-gradient and one copy back instead of host-side subtraction and a host-side optimizer step. Returns None
+        when the mode does not apply or the 12 bytes per parameter are not available."""
+        if not (self.config.outer_state_resident and self._engine_layout and model.device.type == "cuda") or \
+                getattr(self, "_no_device_state", False):
+            return None
+        n = model.master.numel()
+        if self._dev is None or self._dev[0].numel() != n:
+            try:
+                self._dev = tuple(torch.empty(n, dtype=torch.float32, device=model.device) for _ in range(3))
+            except torch.cuda.OutOfMemoryError:
+                self._logger.warning("no room for the outer state on the device (12 bytes per parameter): outer steps use the host path")
+                self._no_device_state, self._dev = True, None
+                return None
+            self._host_changed = True
+        if self._host_changed:
+            self._dev[0].copy_(self.offloaded_data_flat_tensor, non_blocking=True)
+            self._dev[1].copy_(self._momentum_flat(), non_blocking=True)
+            self._host_changed = False
+            self._host_stale = False
+        return self._dev
 
     # ------------------------------------------------------------------ setup
     @torch.no_grad()
@@ -130,18 +168,30 @@ class Diloco:
 
     # ------------------------------------------------------------------ pseudo-gradient
     @torch.no_grad()
-    def _compute_pseudo_gradient(self, model, fake: bool) -> None:
+    def _compute_pseudo_gradient(self, model, fake: bool, scale: float = 1.0) -> None:
+        """offloaded_grad_flat_tensor := (outer - inner) * scale (zeros for a fake step)."""
         if fake:
             self.offloaded_grad_flat_tensor.zero_()
+            self._device_state(model)      # a joiner's first outer step still needs its device copies in place
+            return
+        dev = self._device_state(model)
+        if dev is not None:
+            # outer - inner (and the 1 / workers factor) on the device, one bulk device->host copy of the result
+            torch.sub(dev[0], model.master, out=dev[2])
+            if scale != 1.0:
+                dev[2].mul_(scale)
+            self.offloaded_grad_flat_tensor.copy_(dev[2], non_blocking=False)
             return
         if self._engine_layout:
             # one bulk device->host copy of the whole fp32 shard, then grad = outer - inner on the host
             self.offloaded_grad_flat_tensor.copy_(model.master, non_blocking=False)
             torch.sub(self.offloaded_data_flat_tensor, self.offloaded_grad_flat_tensor, out=self.offloaded_grad_flat_tensor)
-            return
-        for p_off, (_, t) in zip(self.param_list_cpu, _named_local_shards(model)):
-            p_off.grad.copy_(t)
-            torch.sub(p_off.data, p_off.grad, out=p_off.grad)
+        else:
+            for p_off, (_, t) in zip(self.param_list_cpu, _named_local_shards(model)):
+                p_off.grad.copy_(t)
+                torch.sub(p_off.data, p_off.grad, out=p_off.grad)
+        if scale != 1.0:
+            self.offloaded_grad_flat_tensor.mul_(scale)
 
     @torch.no_grad()
     def sync_pseudo_gradient(self, model, fake: bool = False, flag: str = "outer") -> None:
@@ -154,9 +204,8 @@ class Diloco:
         global_pg = edm.global_pg
         self._logger.debug("sync pseudo gradient%s with world size %d", " fake" if fake else "", global_pg.size())
         for attempt in range(self.config.retry_all_reduce):
-            self._compute_pseudo_gradient(model, fake)
+            self._compute_pseudo_gradient(model, fake, 1.0 / global_pg.size())
             try:
-                self.offloaded_grad_flat_tensor.div_(global_pg.size())
                 t_coll = time.perf_counter()
                 edm.monitored_barrier(flag)
                 for j, bucket in enumerate(self._offloaded_grad_grouped_tensor):
@@ -207,11 +256,29 @@ class Diloco:
         if fused is not None and self._engine_layout and model.device.type == "cuda":
             self._fused_step(model, fused, fake, flag)
             return
-        self.sync_pseudo_gradient(model, fake=fake, flag=flag)
-        self._logger.info(f"all reduce pseudo gradient in: {time.perf_counter() - t0} seconds")
+        with self._state_lock:
+            self.sync_pseudo_gradient(model, fake=fake, flag=flag)
+            self._logger.info(f"all reduce pseudo gradient in: {time.perf_counter() - t0} seconds")
+            dev = self._device_state(model) if self.outer_optimizer is not None else None
+            if dev is not None:
+                self._device_outer_update(model, dev)
+                return
         if self.outer_optimizer is not None:
             self.outer_optimizer.step()
         self.sync_inner_model(model)
+
+    def _device_outer_update(self, model, dev) -> None:
+        """Nesterov SGD of the outer parameters on the device copies (what ``torch.optim.SGD(momentum, nesterov=True)``
+        does to the host copies), then inner := outer. The host copies become stale; wait_host_state() refreshes them."""
+        outer, mom, g = dev
+        group = self.outer_optimizer.param_groups[0]
+        lr, mu = float(group["lr"]), float(group["momentum"])
+        g.copy_(self.offloaded_grad_flat_tensor, non_blocking=True)        # the averaged pseudo-gradient
+        mom.mul_(mu).add_(g)
+        outer.sub_(g.add_(mom, alpha=mu), alpha=lr)
+        model.master.copy_(outer)
+        self._host_stale = True
+        model.publish_params()
 
     def _momentum_flat(self) -> torch.Tensor:
         """Flat host view of the SGD momentum buffers (allocated on first use, same layout as the data)."""
@@ -249,9 +316,10 @@ class Diloco:
                 fused = getattr(edm.global_pg, "fused_outer_step", None)
                 if fused is None:
                     break
-        # host path: the host copies are the truth again
+        # host path: the host copies are the truth again (and stay it: no second set of device copies beside the group's)
         self.wait_host_state()
         self._host_changed = True
+        self._no_device_state = True
         self.sync_pseudo_gradient(model, fake=fake, flag=flag)
         self.outer_optimizer.step()
         self.sync_inner_model(model)

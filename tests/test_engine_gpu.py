@@ -148,3 +148,66 @@ def test_peer_wait_runs_out_and_train_step_raises():
         check_status()
     finally:
         lib.pb_set_peer_wait_budget_ns(old)
+
+
+class _OneWorkerMesh:
+    """What Diloco needs from an ElasticDeviceMesh for a single worker whose 'all-reduce' is the identity."""
+
+    class _PG:
+        def size(self):
+            return 1
+
+        def rank(self):
+            return 0
+
+    def __init__(self):
+        self.global_pg = self._PG()
+
+    def maybe_reinit_global_pg(self, *a, **k):
+        return False
+
+    def get_global_pg(self, maybe_reinit=False):
+        return self.global_pg
+
+    def monitored_barrier(self, flag):
+        return None
+
+
+def test_outer_step_with_device_resident_state_matches_host_path(monkeypatch):
+    """With ``outer_state_resident`` the fused engine keeps fp32 outer parameters and momentum on the device, forms the
+    pseudo-gradient there and applies Nesterov there; the host copies are refreshed on demand. Three outer steps must
+    leave the same inner shard, outer parameters and momentum as the host path (host subtraction, torch SGD on the
+    host), and a host copy rewritten in between (as a checkpoint load does) must be picked up."""
+    from prime_b200 import diloco as diloco_mod
+    from prime_b200.config import DilocoConfig
+    from prime_b200.diloco import Diloco
+    monkeypatch.setattr(diloco_mod, "all_reduce", lambda compression, tensor, op, group: None)   # one worker: identity
+    args = _args()
+    engines, dls = [], []
+    for resident in (True, False):
+        eng = FusedLlama(args, device="cuda", ce_chunk_tokens=256)
+        eng.init_weights(seed=3)
+        engines.append(eng)
+        dls.append(Diloco(DilocoConfig(inner_steps=2, outer_state_resident=resident), eng, _OneWorkerMesh()))
+    assert dls[0]._device_state(engines[0]) is not None and dls[1]._device_state(engines[1]) is None
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for step in range(3):
+        delta = torch.randn(engines[0].master.numel(), device="cuda", generator=g) * 1e-3
+        for eng, dl in zip(engines, dls):
+            eng.master.add_(delta)                      # "inner training"
+            dl.step(eng, flag=f"s{step}")
+        if step == 1:                                   # the host copies are rewritten between outer steps
+            for eng, dl in zip(engines, dls):
+                dl.wait_host_state()
+                dl.offloaded_data_flat_tensor.mul_(0.5)
+                dl.mark_host_state_written()
+                eng.master.copy_(dl.offloaded_data_flat_tensor)
+    check_status()
+    dls[0].wait_host_state()
+    assert torch.allclose(engines[0].master, engines[1].master, rtol=0, atol=1e-6)
+    assert torch.allclose(dls[0].offloaded_data_flat_tensor, dls[1].offloaded_data_flat_tensor, rtol=0, atol=1e-6)
+    assert torch.allclose(dls[0]._momentum_flat(), dls[1]._momentum_flat(), rtol=0, atol=1e-6)
+    assert torch.equal(engines[0].master.cpu(), dls[0].offloaded_data_flat_tensor)
+    # the optimizer object that checkpoints serialise sees the refreshed momentum
+    p0 = dls[0].param_list_cpu[0]
+    assert torch.equal(dls[0].outer_optimizer.state[p0]["momentum_buffer"].reshape(-1), dls[0]._momentum_flat()[: p0.numel()])
