@@ -8,8 +8,10 @@
 // (models/llama/model.py:147-156, 168-198, 282-302): KV heads are indexed, never expanded,
 // and the document mask comes from seq_start, not from a BlockMask.
 //
-// One CTA = one 128-row query tile of one head. Roles: warp 0 TMA producer, warp 1 MMA issuer
-// (owns TMEM), warps 2-5 softmax (one thread per query row: row max / sum are thread-local).
+// One CTA = one 128-row query tile of one head, 256 threads in two warpgroups: warp 0 TMA producer, warp 1 MMA
+// issuer (owns TMEM), warps 2-3 only hold the first warpgroup together, warps 4-7 softmax (one thread per query
+// row: row max / sum are thread-local). At head size 64, where two CTAs share an SM, the first warpgroup gives
+// registers up (setmaxnreg) so that a softmax thread can hold its 128-wide score row without spilling.
 //   S = Q K^T            -> TMEM [128 x 128] fp32
 //   P = exp2(S*c - m*c)  -> bf16 pairs in TMEM (tcgen05.st), read by the PV MMA as its A operand
 //   O  += P V            -> TMEM [128 x HD] fp32, accumulated by the MMA across KV tiles; rows are
@@ -41,8 +43,11 @@ struct AttnFwdCfg {
     static constexpr int TMEM_COLS = (HD == 64) ? 256 : 512;
 };
 
+__device__ __forceinline__ void fwd_reg_dealloc_40() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
+__device__ __forceinline__ void fwd_reg_alloc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
+
 template <int HD>
-__global__ void __launch_bounds__(192, (HD == 64 ? 2 : 1))
+__global__ void __launch_bounds__(256, (HD == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     using Cfg = AttnFwdCfg<HD>;
     constexpr int NB = HD / 64;   // 64-column swizzle blocks per tile
@@ -105,97 +110,102 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     const int kv_hi = q_tile;                      // inclusive
     const int n_kv = kv_hi - kv_lo + 1;
 
-    if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            mbar_expect_tx(bar_q, Cfg::TILE_BYTES);
-#pragma unroll
-            for (int b = 0; b < NB; ++b) tma_load_2d(sQ + b * 16384, &tm, bar_q, head * HD + 64 * b, q0);
-        }
-        bool ok = true;
-        for (int j = 0; j < n_kv && ok; ++j) {
-            const int st = j & 1;
-            const uint32_t ph = (j >> 1) & 1;
-            ok = mbar_wait(bar_kvempty + 8 * st, ph ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+    // head size 64: 2 CTAs x (128 x 40 + 128 x 216) registers = the SM's 64 K
+    if (warp < 4) {
+        if (HD == 64) fwd_reg_dealloc_40();
+        if (warp == 0) {
+            // ------------------------------ TMA producer ------------------------------
             if (lane == 0) {
-                const int kv0 = (kv_lo + j) * 128;
-                mbar_expect_tx(bar_kfull + 8 * st, Cfg::TILE_BYTES);
+                mbar_expect_tx(bar_q, Cfg::TILE_BYTES);
 #pragma unroll
-                for (int b = 0; b < NB; ++b)
-                    tma_load_2d(sK + st * Cfg::TILE_BYTES + b * 16384, &tm, bar_kfull + 8 * st, (p.H + kvh) * HD + 64 * b, kv0);
-                mbar_expect_tx(bar_vfull + 8 * st, Cfg::TILE_BYTES);
-#pragma unroll
-                for (int b = 0; b < NB; ++b)
-                    tma_load_2d(sV + st * Cfg::TILE_BYTES + b * 16384, &tm, bar_vfull + 8 * st, (p.H + p.KV + kvh) * HD + 64 * b, kv0);
+                for (int b = 0; b < NB; ++b) tma_load_2d(sQ + b * 16384, &tm, bar_q, head * HD + 64 * b, q0);
             }
-            __syncwarp();
-        }
-        if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(10000);
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
-        constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-        constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
-        auto issue_s = [&](int st) {
-            const uint32_t kb = sK + st * Cfg::TILE_BYTES;
-#pragma unroll
-            for (int k = 0; k < HD / 16; ++k) {
-                const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-                umma_f16_ss(tS, umma_smem_desc(sQ + off, 16, 1024), umma_smem_desc(kb + off, 16, 1024), idesc_s, k ? 1u : 0u);
-            }
-            umma_commit(bar_sfull);
-        };
-        bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            ok = mbar_wait(bar_kfull, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) {
-            tc_fence_after();
-            if (lane == 0) issue_s(0);
-            __syncwarp();
-        }
-        for (int j = 0; j < n_kv && ok; ++j) {
-            const int st = j & 1;
-            const uint32_t ph = (j >> 1) & 1;
-            if (j + 1 < n_kv) {
-                // S_{j+1} is issued as soon as the softmax warps have pulled S_j into registers, so the
-                // tensor core computes it while they do the exponentials of tile j
-                const int st1 = (j + 1) & 1;
-                const uint32_t ph1 = ((j + 1) >> 1) & 1;
-                ok = mbar_wait(bar_sfree, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+            bool ok = true;
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const int st = j & 1;
+                const uint32_t ph = (j >> 1) & 1;
+                ok = mbar_wait(bar_kvempty + 8 * st, ph ^ 1, abort_flag, p.status, PB_ERR_TIMEOUT_EMPTY);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                ok = mbar_wait(bar_kfull + 8 * st1, ph1, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                if (lane == 0) {
+                    const int kv0 = (kv_lo + j) * 128;
+                    mbar_expect_tx(bar_kfull + 8 * st, Cfg::TILE_BYTES);
+#pragma unroll
+                    for (int b = 0; b < NB; ++b)
+                        tma_load_2d(sK + st * Cfg::TILE_BYTES + b * 16384, &tm, bar_kfull + 8 * st, (p.H + kvh) * HD + 64 * b, kv0);
+                    mbar_expect_tx(bar_vfull + 8 * st, Cfg::TILE_BYTES);
+#pragma unroll
+                    for (int b = 0; b < NB; ++b)
+                        tma_load_2d(sV + st * Cfg::TILE_BYTES + b * 16384, &tm, bar_vfull + 8 * st, (p.H + p.KV + kvh) * HD + 64 * b, kv0);
+                }
+                __syncwarp();
+            }
+            if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(10000);
+        } else if (warp == 1) {
+            // ------------------------------ MMA issuer ------------------------------
+            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
+            auto issue_s = [&](int st) {
+                const uint32_t kb = sK + st * Cfg::TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+                    umma_f16_ss(tS, umma_smem_desc(sQ + off, 16, 1024), umma_smem_desc(kb + off, 16, 1024), idesc_s, k ? 1u : 0u);
+                }
+                umma_commit(bar_sfull);
+            };
+            bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                ok = mbar_wait(bar_kfull, 0, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            if (ok) {
+                tc_fence_after();
+                if (lane == 0) issue_s(0);
+                __syncwarp();
+            }
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const int st = j & 1;
+                const uint32_t ph = (j >> 1) & 1;
+                if (j + 1 < n_kv) {
+                    // S_{j+1} is issued as soon as the softmax warps have pulled S_j into registers, so the
+                    // tensor core computes it while they do the exponentials of tile j
+                    const int st1 = (j + 1) & 1;
+                    const uint32_t ph1 = ((j + 1) >> 1) & 1;
+                    ok = mbar_wait(bar_sfree, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_TMEM_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    ok = mbar_wait(bar_kfull + 8 * st1, ph1, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) issue_s(st1);
+                    __syncwarp();
+                }
+                ok = mbar_wait(bar_pfull, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ok = mbar_wait(bar_vfull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) issue_s(st1);
+                if (lane == 0) {
+                    const uint32_t vb = sV + st * Cfg::TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {   // 128 kv rows, 16 per step
+                        // A = P straight from tensor memory: 16 bf16 of every row = 8 columns per K-step
+                        const uint64_t db = umma_smem_desc(vb + k * 2048, 16384, 1024);
+                        umma_f16_ts(tO, tP + k * 8, db, idesc_o, (j | k) ? 1u : 0u);   // O accumulates over all kv tiles
+                    }
+                    umma_commit(bar_ofull);
+                    umma_commit(bar_kvempty + 8 * st);
+                }
                 __syncwarp();
             }
-            ok = mbar_wait(bar_pfull, j & 1, abort_flag, p.status, PB_ERR_TIMEOUT_MISC);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            ok = mbar_wait(bar_vfull + 8 * st, ph, abort_flag, p.status, PB_ERR_TIMEOUT_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t vb = sV + st * Cfg::TILE_BYTES;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {   // 128 kv rows, 16 per step
-                    // A = P straight from tensor memory: 16 bf16 of every row = 8 columns per K-step
-                    const uint64_t db = umma_smem_desc(vb + k * 2048, 16384, 1024);
-                    umma_f16_ts(tO, tP + k * 8, db, idesc_o, (j | k) ? 1u : 0u);   // O accumulates over all kv tiles
-                }
-                umma_commit(bar_ofull);
-                umma_commit(bar_kvempty + 8 * st);
-            }
-            __syncwarp();
         }
     } else {
+        if (HD == 64) fwd_reg_alloc_216();
         // ------------------------------ softmax warps ------------------------------
         // One thread per query row. The whole 128-wide score row is pulled from TMEM in one go and
         // stays in registers; O lives in TMEM (the PV MMA accumulates into it) and is rescaled only
@@ -354,7 +364,7 @@ static int launch_attn_fwd(const CUtensorMap& tm, const AttnFwdParams& p, cudaSt
         configured = true;
     }
     dim3 grid((p.M + 127) / 128, p.H);
-    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(tm, p);
+    kern<<<grid, 256, Cfg::SMEM_BYTES, st>>>(tm, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -30;
 }
 
