@@ -64,9 +64,35 @@ def attention_reference(qkv: torch.Tensor, seq_start: torch.Tensor, H: int, KV: 
 _warned_small_head = False
 
 
+def _padded_hd(hd: int) -> int:
+    """Kernel head size that a head of ``hd`` columns is zero-padded to (0: none fits)."""
+    return 64 if hd < 64 else 128 if hd < 128 else 0
+
+
+def _pad_heads(x: torch.Tensor, n_heads: int, hd: int, to: int) -> torch.Tensor:
+    """[M, n_heads * hd] -> [M, n_heads * to], every head zero-padded on the right."""
+    M = x.shape[0]
+    out = x.new_zeros(M, n_heads, to)
+    out[:, :, :hd] = x.reshape(M, n_heads, hd)
+    return out.view(M, n_heads * to)
+
+
+def _cut_heads(x: torch.Tensor, n_heads: int, hd: int, padded: int) -> torch.Tensor:
+    return x.view(x.shape[0], n_heads, padded)[:, :, :hd].reshape(x.shape[0], n_heads * hd)
+
+
 def _small_head_fwd(qkv, seq_start, H, KV, hd, scale, out):
-    """Head sizes other than 64 / 128 (only the debug presets have them) have no tensor-core
-    kernel; they run the dense fp32 statement on the device."""
+    """Head sizes other than 64 / 128 (the debug presets: 16 and 32). Heads that fit are zero-padded to the next kernel
+    head size, which changes neither the scores nor the real output columns, so these models run the same tcgen05
+    kernels; larger heads run the dense fp32 statement on the device."""
+    to = _padded_hd(hd)
+    if to and hd % 8 == 0:
+        o_p, lse2 = attention_fwd(_pad_heads(qkv, H + 2 * KV, hd, to), seq_start, H, KV, to, scale)
+        o = _cut_heads(o_p, H, hd, to)
+        if out is not None:
+            out.copy_(o)
+            o = out
+        return o, lse2
     global _warned_small_head
     if not _warned_small_head:
         import warnings
@@ -85,7 +111,17 @@ def _small_head_fwd(qkv, seq_start, H, KV, hd, scale, out):
     return o, lse2
 
 
-def _small_head_bwd(qkv, dout, seq_start, H, KV, hd, scale, dqkv, rope_table, seq_len):
+def _small_head_bwd(qkv, o, dout, lse2, seq_start, H, KV, hd, scale, dqkv, rope_table, seq_len, row_dots):
+    to = _padded_hd(hd)
+    if to and hd % 8 == 0:
+        g_p = attention_bwd(_pad_heads(qkv, H + 2 * KV, hd, to), _pad_heads(o, H, hd, to), _pad_heads(dout, H, hd, to), lse2,
+                            seq_start, H, KV, to, scale, row_dots=row_dots)
+        g = _cut_heads(g_p, H + 2 * KV, hd, to).contiguous()
+        if rope_table is not None:      # the kernel's own inverse rotation pairs columns of the padded head: done here instead
+            from .kernels import rope_
+            g = rope_(g, rope_table, seq_len, H + KV, hd, backward=True)
+        dqkv.copy_(g)
+        return dqkv
     with torch.enable_grad():
         x = qkv.detach().float().requires_grad_(True)
         ref = attention_reference(x, seq_start, H, KV, hd, scale)
@@ -154,7 +190,7 @@ def attention_bwd(qkv: torch.Tensor, o: torch.Tensor, dout: torch.Tensor, lse2: 
         return dqkv
     assert dout.stride(1) == 1 and o.stride(1) == 1 and dqkv.stride(1) == 1
     if hd not in (64, 128):
-        return _small_head_bwd(qkv, dout, seq_start, H, KV, hd, scale, dqkv, rope_table, seq_len)
+        return _small_head_bwd(qkv, o, dout, lse2, seq_start, H, KV, hd, scale, dqkv, rope_table, seq_len, row_dots)
     dq_acc = _scratch_buf(qkv.device, "attn_dq", M * H * hd)
     D = row_dots if row_dots is not None else _scratch_buf(qkv.device, "attn_D", M * H)
     tiles = _scratch_buf(qkv.device, "attn_tiles", (M + 127) // 128 + 1, torch.int32)

@@ -108,3 +108,29 @@ def test_attention_bwd_more_items_than_sms(B, T, H, KV, hd, packed):
     assert _rel(got, gref) < 3e-2
     # dQ is summed by reduce-adds whose order depends on which CTA drew which item, so two launches agree to rounding
     assert _rel(again, got) < 1e-3
+
+
+@pytest.mark.parametrize("hd,KV", [(32, 2), (16, 4), (96, 1)])
+def test_attention_small_heads_run_the_kernels_zero_padded(hd, KV):
+    """Head sizes below the kernels' 64 / 128 (the debug presets use 16 and 32) are zero-padded per head and run the
+    same tcgen05 kernels; output, log-sum-exp and gradients (with the inverse rotation applied outside) match the dense
+    fp32 statement."""
+    from prime_b200 import native
+    B, T, H = 2, 256, 4
+    qkv, ss = _case(B, T, H, KV, hd, packed=True, seed=5)
+    native.launch_counter_reset()
+    o, lse2 = A.attention_fwd(qkv, ss, H, KV, hd)
+    assert native.launch_counter() >= 1                      # the attention kernel ran (the dense fallback launches none of ours)
+    ref = A.attention_reference(qkv.float(), ss, H, KV, hd)
+    assert o.shape == (B * T, H * hd) and _rel(o, ref) < 2e-2
+    _, lse_ref = A.attention_fwd(qkv.cpu(), ss.cpu(), H, KV, hd)
+    assert torch.allclose(lse2.cpu(), lse_ref, atol=5e-2)
+    dout = (torch.randn(B * T, H * hd, device="cuda") * 0.5).bfloat16()
+    table = ops.rope_table(T, hd, 10000.0, "cuda")
+    g = A.attention_bwd(qkv, o, dout, lse2, ss, H, KV, hd, rope_table=table, seq_len=T)
+    torch.cuda.synchronize()
+    ops.check_status()
+    x = qkv.float().requires_grad_(True)
+    (gref,) = torch.autograd.grad(A.attention_reference(x, ss, H, KV, hd), x, dout.float())
+    gref = ops.rope_(gref.bfloat16().contiguous(), table, T, H + KV, hd, backward=True)
+    assert _rel(g, gref) < 3e-2
