@@ -182,6 +182,10 @@ class NvlinkWorkerGroup:
                 outer.copy_(outer_host, non_blocking=True)
                 mom.copy_(mom_host, non_blocking=True)
             ev[1].record()
+            if resident:
+                # from here on the device copies are the truth: if the exchange below fails before it changes them, the
+                # caller's fallback can still bring the host copies up to date (wait_host_copies)
+                self._refresh_args = (outer, mom, outer_host, mom_host, ev[1])
             if compression == Compression.UINT8:
                 self._run(n, outer, inner, 1.0 / self.size(), fake, outer=outer, inner=inner, mom=mom, lr=lr, mu=momentum)
             else:
@@ -206,15 +210,15 @@ class NvlinkWorkerGroup:
             self.last_timing_ms = {"h2d": ev[0].elapsed_time(ev[1]) if staged_in else 0.0, "exchange_update": ev[1].elapsed_time(ev[2]),
                                    "d2h": 0.0 if resident else ev[2].elapsed_time(ev[3]), "resident": bool(resident)}
             # a peer wait that gave up raises here. The update kernel skips its work in that case, so the device copies
-            # still hold the state from before this step, and _refresh_args (set above) lets the caller's fallback path
-            # bring the host copies up to date from them.
+            # still hold the state from before this step, and _refresh_args lets the caller's fallback path bring the
+            # host copies up to date from them.
             check_status(self.device)
 
     def wait_host_copies(self) -> None:
         """Resident mode: bring the pinned host copies of the outer state up to date with the device copies, if an outer
         step has run since they were last written. Called by whoever is about to read them (checkpoint save, live
-        recovery, the hash log) and at the start of the next outer step; an outer step itself never copies back, so
-        neither it nor the inner steps that follow share a copy engine with gigabytes of transfer."""
+        recovery, the hash log); an outer step itself never copies back, so neither it nor the inner steps that follow
+        share a copy engine with gigabytes of transfer."""
         with self._host_lock:
             args = getattr(self, "_refresh_args", None)
             if args is None:
