@@ -1,5 +1,6 @@
-"""DiLoCo: local AdamW inner steps, Nesterov-SGD outer steps on the averaged pseudo-gradient, with
-the outer state kept in (pinned) host memory (reference: src/zeroband/diloco.py:24-215).
+"""DiLoCo: local AdamW inner steps, Nesterov-SGD outer steps on the averaged pseudo-gradient. The outer state has
+pinned host copies as in the reference (src/zeroband/diloco.py:24-215); with the fused engine on CUDA the working
+copies live in device memory and the host copies are written when something reads them.
 
 Public surface kept from the reference: ``Diloco(config, model, elastic_device_mesh)``,
 ``step(model, fake, flag)``, ``sync_pseudo_gradient``, ``sync_inner_model``, ``get_offloaded_param``
@@ -17,6 +18,11 @@ Design differences from the reference:
   * a worker group that offers ``fused_outer_step`` (NVLink peers inside one box,
     parallel/diloco_comm.py) runs pseudo-gradient, int8 all-reduce and the Nesterov update in one
     GPU kernel sequence; the host path below is used for TCP rings and torch process groups;
+  * on that host path with the fused engine on CUDA (``diloco.outer_state_resident``, default on) the pseudo-gradient is
+    formed on the device, only it crosses to the host for the exchange and back, and the Nesterov update runs on device
+    copies of outer parameters and momentum; ``wait_host_state()`` refreshes ``param_list_cpu`` and the outer optimizer's
+    momentum buffers on demand (checkpoint save, live recovery, hash log) and ``mark_host_state_written()`` tells this
+    class that somebody rewrote them (checkpoint load, live recovery);
   * ``fake=True`` (a freshly joined worker) contributes a zero pseudo-gradient but still receives
     the average, as the reference's README describes.
 """

@@ -4,9 +4,10 @@ over symmetric memory, for workers that live in the same NVSwitch domain.
 ``NvlinkWorkerGroup`` plays the role of the cross-worker process group: ``size() / rank() /
 barrier()``, ``all_reduce_tensor`` (used by :func:`prime_b200.collectives.all_reduce`) and
 ``fused_outer_step`` (picked up by :class:`prime_b200.diloco.Diloco`), all backed by the kernels in
-csrc/diloco_comm.cu. The outer parameters and momentum stay in pinned host memory between outer
-steps and are staged to HBM only for the duration of the fused step
-(reference: src/zeroband/diloco.py:77-144, 203-215 does the whole outer step on the CPU over gloo).
+csrc/diloco_comm.cu. The fp32 outer parameters and momentum either stay resident in HBM between outer
+steps, with the pinned host copies written on demand (``resident=True``, the default of
+``diloco.outer_state_resident``), or live in pinned host memory and are staged to HBM for the duration of
+the fused step (reference: src/zeroband/diloco.py:77-144, 203-215 does the whole outer step on the CPU over gloo).
 """
 from __future__ import annotations
 
