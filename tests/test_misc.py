@@ -320,3 +320,28 @@ def test_engine_flag_checks():
     _check_engine_flags(mk(), True, log)                    # defaults: nothing to say
     _check_engine_flags(mk(attn_fn="math"), False, log)     # eager path honours attn_fn
     assert not seen
+
+
+def test_bench_allreduce_arms_print_one_json_line_on_cpu_ranks():
+    """``bench.py --config allreduce --impl reference`` runs on CPU ranks over gloo (that is where the reference's outer
+    all-reduce runs): two ranks, one small size. It prints one JSON line that either holds the reference ring's row or
+    says in one line why the reference is unavailable; the same line shape as the GPU arms."""
+    import json
+    import subprocess
+    import sys
+    from prime_b200.utils import get_random_available_port
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(get_random_available_port()), os.path.join(root, "bench.py"), "--gpus", "2", "--config", "allreduce",
+           "--impl", "reference", "--sizes-mb", "1"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+    assert out.returncode == 0 and len(lines) == 1, out.stderr[-2000:]
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference"
+    if "unavailable" in d:
+        assert isinstance(d["unavailable"], str) and d["unavailable"]
+    else:
+        assert d["n_gpus"] == 2 and d["higher_is_better"] is False
+        row = d["rows"][0]
+        assert row["ref_py_uint8_ring"]["rel_err"] < 0.1 and row["gloo_fp32"]["rel_err"] < 1e-6
