@@ -5,7 +5,7 @@ top-k retention, remote push and live recovery for joining workers
 
 On-disk layout (unchanged, so checkpoints interchange and the HF exporter works)::
 
-    {ckpt.path}/step_{N}/.metadata, __{rank}_0.distcp ...   dcp.save({"model","optimizer","scheduler","training_progress"})
+    {ckpt.path}/step_{N}/.metadata, __{rank}_{i}.distcp ... dcp.save({"model","optimizer","scheduler","training_progress"})
     {ckpt.path}/step_{N}/__{local_rank}_0.pt                {"optimizer": outer SGD state, local tensors}
     {ckpt.path}/step_{N}/data/_{local_rank}.pt              {"data_loader": dataloader.state_dict()}
     {ckpt.remote.path}/step_{N}/...                         copy of the above
@@ -386,7 +386,12 @@ class CkptManager:
             if quiet:
                 warnings.simplefilter("ignore")
             os.makedirs(ckpt_path, exist_ok=True)
-            dcp.save(self.states, checkpoint_id=ckpt_path, process_group=self.process_group)
+            # several writer threads per rank (every parameter shard is an item of its own), and no fsync for files
+            # that land in the in-memory staging directory: the blocking part of a save is this call
+            staged = self.use_staging and ckpt_path.startswith(SHM_ROOT)
+            writer = dcp.FileSystemWriter(ckpt_path, thread_count=max(1, int(os.environ.get("PRIME_B200_CKPT_WRITER_THREADS", "4"))),
+                                          sync_files=not staged)
+            dcp.save(self.states, storage_writer=writer, process_group=self.process_group)
             if self.diloco_offloaded_optimizer is not None:
                 if self.diloco is not None:
                     self.diloco.wait_host_state()      # the host copy of the outer momentum may still be on its way
