@@ -576,7 +576,11 @@ class ElasticDeviceMesh:
             return False
         t0 = time.perf_counter()
         if self._global_leader:
-            self._resolve_world(admit_joiners=admit_joiners)
+            changed = self._resolve_world(admit_joiners=admit_joiners)
+            if _depth > 0 and not changed:
+                # a retry after a failed group creation with unchanged membership: move to a fresh store prefix, so that
+                # nobody reads the rendezvous keys (addresses of sockets that are closed by now) the failed attempt left
+                self.global_store.set("mesh_count", str(int(self._get("mesh_count")) + 1))
             self._resolve_seq += 1
             self.global_store.set("resolved_time", f"{self._resolve_seq}:{uuid4().hex}")
         else:
