@@ -106,7 +106,11 @@ class EagerBackend:
 
 class FusedBackend:
     """Adapter around :class:`FusedLlama`. ``scheduler`` is a ``LambdaLR`` on a one-parameter dummy
-    optimizer: it only produces the learning rate the sharded AdamW kernel is launched with."""
+    optimizer: it only produces the learning rate the sharded update is launched with. With ``optim.type = "adam"`` the
+    update is the engine's sharded AdamW kernel; with ``"soap"`` it is :class:`prime_b200.optimizers.SOAP` stepping this
+    rank's fp32 shards (``FusedLlama.set_shard_optimizer``): forward, backward, reduce-scatter, clip and the bf16 all-gather
+    stay on the engine's kernels, and every rank preconditions its own block of rows, as the reference's fully-sharded
+    Shampoo does (src/zeroband/optimizers.py:31-48)."""
 
     def __init__(self, engine, optim_cfg, sched_factory, mesh=None, max_norm: float = 1.0):
         self.engine = engine
@@ -118,6 +122,14 @@ class FusedBackend:
         self.max_norm = max_norm
         self.device = engine.device
         self.is_fused = True
+        self.shard_optimizer = None
+        if getattr(optim_cfg, "type", "adam") == "soap":
+            from .optimizers import SOAP
+            c = optim_cfg
+            self.shard_optimizer = engine.set_shard_optimizer(lambda params: SOAP(
+                params, lr=c.lr, betas=(c.betas1, c.betas2), eps=1e-12, weight_decay=c.weight_decay,
+                max_preconditioner_dim=c.max_preconditioner_dim, precondition_frequency=c.precondition_frequency))
+            self.shard_optimizer.materialize_state()      # checkpoints load in place: the state must exist before the first step
 
     # surface used by Diloco
     def named_master_shards(self):
@@ -138,6 +150,7 @@ class FusedBackend:
         loss, norm = self.engine.train_step(batch["input_ids"], batch["labels"], self.current_lr(), micro_bs=micro_bs,
                                             betas=(c.betas1, c.betas2), weight_decay=c.weight_decay, max_norm=self.max_norm,
                                             seq_start=batch.get("seq_start"), sync_loss=True)
+        self.optimizer.step()          # the dummy optimizer only carries the schedule; stepping it keeps the scheduler's bookkeeping quiet
         self.lr_scheduler.step()
         z = float(self.engine._ws["step.loss"][1]) if self.engine.z_weight else 0.0
         return {"loss": loss, "z_loss": z, "grad_norm": norm}
@@ -166,9 +179,25 @@ class FusedBackend:
         # DCP loads in place into the DTensor locals, which are views of the master shard
         self.engine.publish_params()
 
+    def _soap_key(self, i: int, k: str) -> str:
+        # the state of a shard optimizer belongs to this rank's rows (its factors have the shard's shape, not a slice of a
+        # global tensor's), so it is stored under keys of this rank
+        return f"state.rank{self.engine.rank}.{self.engine.layout.params[i].name}.{k}"
+
     def optimizer_state_dict(self) -> dict[str, Any]:
         eng, c = self.engine, self.cfg
         out: dict[str, Any] = {}
+        if self.shard_optimizer is not None:
+            out["state.step"] = torch.tensor(float(eng.opt_step))
+            for i, q in enumerate(eng._shard_params):
+                for k, v in self.shard_optimizer.state.get(q, {}).items():
+                    if v is None:                                # a side wider than max_preconditioner_dim: identity factor
+                        continue
+                    if torch.is_tensor(v):
+                        out[self._soap_key(i, k)] = v
+                    else:
+                        out[self._soap_key(i, k)] = torch.tensor(float(v))
+            return out
         for p in eng.layout.params:
             out[f"state.{p.name}.step"] = torch.tensor(float(eng.opt_step))
             out[f"state.{p.name}.exp_avg"] = self._dt(eng.exp_avg, p.name)
@@ -179,6 +208,16 @@ class FusedBackend:
         return out
 
     def load_optimizer_state_dict(self, sd: dict[str, Any]) -> None:
+        if self.shard_optimizer is not None:
+            # DCP loads tensors in place into the objects optimizer_state_dict() handed out; plain numbers come back here
+            step = sd.get("state.step")
+            if step is not None:
+                self.engine.opt_step = int(float(step))
+            for i, q in enumerate(self.engine._shard_params):
+                st = self.shard_optimizer.state.get(q)
+                if st is not None and self._soap_key(i, "step") in sd:
+                    st["step"] = int(float(sd[self._soap_key(i, "step")]))
+            return
         first = self.engine.layout.params[0].name
         step = sd.get(f"state.{first}.step")
         if step is not None:

@@ -152,6 +152,7 @@ class FusedLlama:
         self._reduced_groups: set[int] = set()      # groups whose reduce-scatter is already in flight on the comm stream
         self.overlap_reduce = True                  # False: every group is reduced after the backward, on the main stream
         self._reduce_in_backward = False
+        self._shard_opt = None         # set_shard_optimizer(): a torch optimizer on the shards instead of the AdamW kernel
         self._norm_local = torch.zeros(8, dtype=torch.float32, device=dev)
         self._norm_global = torch.zeros(8, dtype=torch.float32, device=dev)
         self.opt_step = 0
@@ -328,6 +329,32 @@ class FusedLlama:
     def named_master_shards(self):
         for p in self.layout.params:
             yield p.name, self.shard_view(self.master, p.name)
+
+    def set_shard_optimizer(self, factory) -> torch.optim.Optimizer:
+        """Replace the sharded AdamW kernel by a ``torch.optim.Optimizer`` that works on this rank's shards: ``factory``
+        gets one ``nn.Parameter`` per model parameter whose data is the rank's dim-0 slice of the fp32 master weights
+        (a view, so the update lands in place) and whose ``.grad`` is the matching view of the reduced, averaged fp32
+        gradient shard. The engine still does forward / backward, the reduce-scatter, the global-norm clip and the bf16
+        all-gather; the optimizer sees exactly what FSDP2 would hand a sharded optimizer (each rank's rows of every
+        parameter), which is how a fully-sharded Shampoo / SOAP preconditions: per rank, on its own block of rows."""
+        params = []
+        for name, shard in self.named_master_shards():
+            q = torch.nn.Parameter(shard, requires_grad=True)
+            q.grad = self.shard_view(self.grad_shard, name)
+            params.append(q)
+        self._shard_params = params
+        self._shard_opt = factory([q for q in params if q.numel() > 0])
+        return self._shard_opt
+
+    def _shard_optimizer_update(self, lr: float, max_norm: float) -> None:
+        """grad_shard holds this rank's averaged fp32 gradients and _norm_global[0] the squared global norm."""
+        if max_norm > 0:
+            coef = (max_norm / (self._norm_global[0].sqrt() + 1e-6)).clamp(max=1.0)
+            self.grad_shard.mul_(coef)
+        for group in self._shard_opt.param_groups:
+            group["lr"] = lr
+        self._shard_opt.step()
+        self.publish_params()          # bf16 copies of the new master rows into every rank's replica
 
     @torch.no_grad()
     def load_from_module(self, model: torch.nn.Module) -> None:
@@ -630,6 +657,11 @@ class FusedLlama:
         self._reduced_groups.clear()
         K.sum_f32(self._norm_parts, self._norm_local[0:1])
         self.comm.allreduce_scalars(self._norm_local, self._norm_global, 1)   # also orders: all ranks done reading grads
+        if self._shard_opt is not None:
+            assert not self.reshard, "a shard optimizer needs the resident replica (publish_params refreshes it)"
+            self._shard_optimizer_update(lr, max_norm)
+            self._accum = False
+            return self._norm_global[0].sqrt()
         if self.reshard:
             # no replica to refresh: the new bf16 values go to this rank's own rows only (a one-rank "push")
             n = self.master.numel()
@@ -692,6 +724,11 @@ class FusedLlama:
             self.grad_shard[s.shard_offset: s.shard_offset + s.numel].copy_(self.grads[s.full_offset: s.full_offset + s.numel])
         K.sumsq(self.grad_shard, self._norm_global[0:1])
         norm = self._norm_global[0].sqrt()
+        if self._shard_opt is not None:
+            norm = norm.clone()
+            self._shard_optimizer_update(lr, max_norm)
+            self._accum = False
+            return norm
         K.adamw_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, None, lr, betas[0], betas[1], eps, weight_decay,
                  self.opt_step, gnorm=norm if max_norm > 0 else None, max_norm=max_norm)
         self.publish_params()

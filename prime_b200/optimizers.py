@@ -50,6 +50,30 @@ class SOAP(torch.optim.Optimizer):
         _, v = torch.linalg.eigh(a)
         return v.flip(1).to(m.dtype)
 
+    @staticmethod
+    def _init_state(st: dict, local: torch.Tensor, max_dim: int, with_bases: bool) -> None:
+        st["step"] = 0
+        st["exp_avg"] = torch.zeros_like(local)
+        st["exp_avg_sq"] = torch.zeros_like(local)
+        if local.dim() >= 2:
+            g2 = local.reshape(local.shape[0], -1)
+            for side, n in (("L", g2.shape[0]), ("R", g2.shape[1])):
+                keep = n <= max_dim
+                st["GG_" + side] = torch.zeros(n, n, dtype=torch.float32, device=local.device) if keep else None
+                # the first step replaces the basis by the eigenvectors of the first statistics; a placeholder of the right
+                # shape only matters to a checkpoint loader that fills existing tensors in place
+                st["Q_" + side] = torch.eye(n, dtype=torch.float32, device=local.device) if (keep and with_bases) else None
+
+    @torch.no_grad()
+    def materialize_state(self) -> None:
+        """Create every parameter's state now (zeros, identity bases) instead of at its first step, so that a checkpoint
+        loader that loads in place finds tensors of the final shapes."""
+        for group in self.param_groups:
+            for p in group["params"]:
+                if not self.state[p]:
+                    local = p._local_tensor if hasattr(p, "_local_tensor") else p
+                    self._init_state(self.state[p], local.detach().float(), group["max_preconditioner_dim"], with_bases=True)
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
@@ -67,15 +91,7 @@ class SOAP(torch.optim.Optimizer):
                 target = p._local_tensor if hasattr(p, "_local_tensor") else p
                 st = self.state[p]
                 if not st:
-                    st["step"] = 0
-                    st["exp_avg"] = torch.zeros_like(local)
-                    st["exp_avg_sq"] = torch.zeros_like(local)
-                    if local.dim() >= 2:
-                        g2 = local.reshape(local.shape[0], -1)
-                        for side, n in (("L", g2.shape[0]), ("R", g2.shape[1])):
-                            st["GG_" + side] = (torch.zeros(n, n, dtype=torch.float32, device=local.device)
-                                                if n <= group["max_preconditioner_dim"] else None)
-                            st["Q_" + side] = None
+                    self._init_state(st, local, group["max_preconditioner_dim"], with_bases=False)
                 st["step"] += 1
                 t = st["step"]
                 if wd:

@@ -165,8 +165,15 @@ def train(config: Config) -> None:
     sched = partial(get_scheduler, config.optim.sched_type, num_warmup_steps=config.optim.warmup_steps,
                     num_stable_steps=config.optim.stable_steps, num_training_steps=config.optim.total_steps)
     z_weight = config.optim.z_loss_weight if config.optim.z_loss else None
-    fused_path = use_cuda and config.optim.optim.type == "adam"
+    # both optimizers run on the fused engine: AdamW as its sharded kernel, SOAP as a shard optimizer on the engine's fp32
+    # row shards (every rank preconditions its own rows; see FusedBackend)
+    fused_path = use_cuda and config.optim.optim.type in ("adam", "soap")
     _check_engine_flags(config, fused_path, logger)
+    want_reshard = "reshard_after_forward" in config.train.model_fields_set and config.train.reshard_after_forward
+    if fused_path and want_reshard and config.optim.optim.type == "soap":
+        logger.warning("train.reshard_after_forward has no effect with optim.type = soap: the shard optimizer refreshes the resident "
+                       "bf16 replica after its step")
+        want_reshard = False
     with sw.record_block("Get Model"):
         if fused_path:
             from .engine.fused_llama import FusedLlama
@@ -177,7 +184,7 @@ def train(config: Config) -> None:
                 comm = SymmComm(elastic_device_mesh.local_pg, device)
             engine = FusedLlama(margs, device=device, comm=comm,
                                 grad_dtype=torch.float32 if config.train.reduce_fp32 else torch.bfloat16,
-                                reshard=("reshard_after_forward" in config.train.model_fields_set and config.train.reshard_after_forward),
+                                reshard=want_reshard,
                                 ac_ckpt=config.train.ac_ckpt, z_mode=K.Z_LSE if (z_weight and config.train.fused_linear_ce) else
                                 (K.Z_MAX if z_weight else K.Z_NONE), z_weight=z_weight or 0.0)
             torch.manual_seed(42)

@@ -161,3 +161,60 @@ def test_optimizer_cta_ranges_cover_every_segment():
                 share = x / total * grid if total else 0.0
                 if share >= 4.0:                # large segments get about their share of the grid
                     assert 0.5 * share <= width <= 1.5 * share + 1
+
+
+def test_soap_runs_as_a_shard_optimizer_of_the_fused_engine(tmp_path):
+    """``optim.type = "soap"`` with the fused engine: the engine produces the reduced fp32 gradient shard and the global
+    norm, SOAP steps the fp32 master shards in place, the bf16 replica is refreshed. Checked against SOAP applied by hand
+    to copies of the same shards with the same clipped gradients, over enough steps to cross a basis refresh; then the
+    optimizer state round-trips through the flat state dict a checkpoint uses."""
+    from prime_b200.backend import FusedBackend
+    from prime_b200.config import SoapConfig
+    from prime_b200.lr_scheduler import get_scheduler
+    from prime_b200.optimizers import SOAP
+    args = ModelArgs(dim=64, n_layers=2, n_heads=4, n_kv_heads=2, ffn_hidden=128, vocab_size=200, max_seq_len=32,
+                     init_mode="normal", init_std=0.05)
+    cfg = SoapConfig(lr=3e-3, weight_decay=0.01, precondition_frequency=3, max_preconditioner_dim=256)
+    eng = FusedLlama(args, device="cpu", grad_dtype=torch.float32, ce_chunk_tokens=64)
+    eng.init_weights(seed=2)
+    backend = FusedBackend(eng, cfg, lambda o: get_scheduler("cosine", o, 1, 0, 100), max_norm=0.5)
+    assert backend.shard_optimizer is not None and eng._shard_opt is backend.shard_optimizer
+    # the hand-run twin: copies of the shards, their own SOAP
+    twin = [torch.nn.Parameter(t.clone()) for _, t in eng.named_master_shards()]
+    opt = SOAP(twin, lr=cfg.lr, betas=(cfg.betas1, cfg.betas2), eps=1e-12, weight_decay=cfg.weight_decay,
+               max_preconditioner_dim=cfg.max_preconditioner_dim, precondition_frequency=cfg.precondition_frequency)
+    g = torch.Generator().manual_seed(0)
+    losses = []
+    for step in range(5):
+        tok = torch.randint(0, args.vocab_size, (2, 33), generator=g)
+        batch = {"input_ids": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()}
+        lr = backend.current_lr()
+        out = backend.train_step(batch, micro_bs=2)
+        losses.append(out["loss"])
+        # grad_shard still holds the clipped gradients the shard optimizer consumed
+        for q, (name, _) in zip(twin, eng.named_master_shards()):
+            q.grad = eng.shard_view(eng.grad_shard, name).clone()
+        for group in opt.param_groups:
+            group["lr"] = lr
+        opt.step()
+        for q, (name, t) in zip(twin, eng.named_master_shards()):
+            assert torch.allclose(q.data, t, rtol=1e-5, atol=1e-6), (step, name)
+        # the bf16 replica follows the master shard
+        name0, t0 = next(iter(eng.named_master_shards()))
+        assert torch.allclose(eng.w[name0].float(), t0, atol=2e-2)
+    assert out["grad_norm"] > 0 and all(torch.isfinite(torch.tensor(losses)))
+    # state dict: every tensor of the shard optimizer's state, keyed by rank and parameter; loading fills them in place
+    sd = backend.optimizer_state_dict()
+    assert any(k.endswith(".Q_L") for k in sd) and any(k.endswith(".GG_R") for k in sd) and "state.step" in sd
+    saved = {k: v.clone() for k, v in sd.items()}
+    eng2 = FusedLlama(args, device="cpu", grad_dtype=torch.float32, ce_chunk_tokens=64)
+    eng2.init_weights(seed=2)
+    backend2 = FusedBackend(eng2, cfg, lambda o: get_scheduler("cosine", o, 1, 0, 100), max_norm=0.5)
+    sd2 = backend2.optimizer_state_dict()
+    assert set(sd2) == set(sd)
+    for k, v in sd2.items():
+        v.copy_(saved[k])                     # what the checkpoint loader does
+    backend2.load_optimizer_state_dict(sd2)
+    assert eng2.opt_step == eng.opt_step
+    q0 = eng2._shard_params[0]
+    assert backend2.shard_optimizer.state[q0]["step"] == 5

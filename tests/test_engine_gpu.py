@@ -211,3 +211,40 @@ def test_outer_step_with_device_resident_state_matches_host_path(monkeypatch):
     # the optimizer object that checkpoints serialise sees the refreshed momentum
     p0 = dls[0].param_list_cpu[0]
     assert torch.equal(dls[0].outer_optimizer.state[p0]["momentum_buffer"].reshape(-1), dls[0]._momentum_flat()[: p0.numel()])
+
+
+def test_soap_shard_optimizer_on_gpu():
+    """``optim.type = "soap"`` on the GPU: gradients, reduce and clip come from the engine's kernels, SOAP steps the fp32
+    shards with torch's CUDA ops, the bf16 replica is refreshed by the push kernel. Same check as on the CPU: a hand-run
+    SOAP on copies of the shards, fed the clipped gradient shard, stays equal to the engine's master weights."""
+    from prime_b200.backend import FusedBackend
+    from prime_b200.config import SoapConfig
+    from prime_b200.lr_scheduler import get_scheduler
+    from prime_b200.optimizers import SOAP
+    args = _args()
+    cfg = SoapConfig(lr=2e-3, weight_decay=0.01, precondition_frequency=2, max_preconditioner_dim=1024)
+    eng = FusedLlama(args, device="cuda", ce_chunk_tokens=512)
+    eng.init_weights(seed=4)
+    backend = FusedBackend(eng, cfg, lambda o: get_scheduler("cosine", o, 1, 0, 100), max_norm=1.0)
+    twin = [torch.nn.Parameter(t.clone()) for _, t in eng.named_master_shards()]
+    opt = SOAP(twin, lr=cfg.lr, betas=(cfg.betas1, cfg.betas2), eps=1e-12, weight_decay=cfg.weight_decay,
+               max_preconditioner_dim=cfg.max_preconditioner_dim, precondition_frequency=cfg.precondition_frequency)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, args.vocab_size, (4, 257), generator=g)
+    batch = {"input_ids": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()}
+    losses = []
+    for step in range(4):
+        lr = backend.current_lr()
+        out = backend.train_step(batch, micro_bs=2)
+        losses.append(out["loss"])
+        for q, (name, _) in zip(twin, eng.named_master_shards()):
+            q.grad = eng.shard_view(eng.grad_shard, name).clone()
+        for group in opt.param_groups:
+            group["lr"] = lr
+        opt.step()
+        for q, (name, t) in zip(twin, eng.named_master_shards()):
+            assert torch.allclose(q.data, t, rtol=1e-3, atol=1e-4), (step, name)
+    check_status()
+    assert losses[-1] < losses[0]
+    name0, t0 = next(iter(eng.named_master_shards()))
+    assert torch.allclose(eng.w[name0].float(), t0, atol=2e-2)
